@@ -1,0 +1,512 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 quantized GEMM suite.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One JSON line on stdout (rank 0).  A *step* is one pass of the hot path over one batch of
+synthetic input: one GEMM of the workload's shape (plus, on N > 1 GPUs, the all-gather of C).
+
+Workloads
+  bf16_8192   bf16 GEMM M=N=K=8192, N(0,1) inputs, fp32 accumulate, bf16 out   (default)
+  int8_8192   int8 GEMM M=N=K=8192, uniform [-127,127], int32 out
+  fp16_8192   fp16 GEMM M=N=K=8192
+  int8_4096   int8 GEMM M=N=K=4096
+  w8a8        int8 W8A8 linear M=8192, N=28672, K=8192, per-row/per-column scales, bf16 out
+
+On N > 1 GPUs (launched by torchrun, one rank per GPU) the rows of A are split across the ranks,
+B is replicated, every rank computes its [M/N_gpus, N] slab of C in place inside a full [M, N]
+buffer and an NCCL all-gather completes C on every rank; total work is fixed ("strong").
+
+`value` is whole-job throughput with inputs resident in HBM; `e2e` is the same metric through
+the host-buffer C entry point (pinned host memory, copies inside the timed region).
+`--impl reference` times the reference's own CPU loop (matrixMulCPU, compiled unmodified into
+oracle/_ref/) on the host cores instead; see reference_arm() for how the sample is bounded.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (kind, M, N, K, in_bytes, out_bytes, unit)
+    "bf16_8192": ("bf16", 8192, 8192, 8192, 2, 2, "TFLOP/s"),
+    "fp16_8192": ("f16", 8192, 8192, 8192, 2, 2, "TFLOP/s"),
+    "int8_8192": ("i8", 8192, 8192, 8192, 1, 4, "TOP/s"),
+    "int8_4096": ("i8", 4096, 4096, 4096, 1, 4, "TOP/s"),
+    "w8a8": ("w8a8", 8192, 28672, 8192, 1, 2, "TOP/s"),
+}
+NOMINAL_PEAK = {"bf16": 2250.0, "f16": 2250.0, "i8": 4500.0, "w8a8": 4500.0}  # dense, per GPU
+METRIC = "int8 TOPS & bf16/fp16 TFLOPS per GPU at 8192^3; % of dense tensor peak"
+
+# DRAM bytes per launch of the dominant kernel measured by ncu (dram__bytes_read.sum +
+# dram__bytes_write.sum); None until a capture of that workload is summarised under profiles/.
+NCU_TRAFFIC_BYTES = {}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "burst": d["bf16_tflops"], "sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "burst": 1590.0, "sustained": 1400.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------- clock sampling
+
+class ClockSampler:
+    """Samples SM clock and clock-event reasons of one GPU through NVML while a region runs."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
+
+    def __init__(self, torch_device_index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(torch_device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # no NVML: the line will say so
+            self._nvml, self._h, self.error = None, None, repr(e)
+
+    def _loop(self):
+        nv, h = self._nvml, self._h
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if self._nvml is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "error": getattr(self, "error", "no nvml")}
+        s = sorted(self.samples)
+        med = s[len(s) // 2] if s else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ----------------------------------------------------------------------------- workload set-up
+
+def make_inputs(kind, M_local, N, K, device, seed):
+    """Seeded synthetic inputs of the workload's distributions, resident on the device."""
+    import torch
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    extra = {}
+    if kind in ("bf16", "f16"):
+        dt = torch.bfloat16 if kind == "bf16" else torch.float16
+        a = torch.randn((M_local, K), device=device, generator=g).to(dt)
+        b = torch.randn((K, N), device=device, generator=torch.Generator(device=device).manual_seed(999)).to(dt)
+    elif kind == "i8":
+        a = torch.randint(-127, 128, (M_local, K), dtype=torch.int8, device=device, generator=g)
+        b = torch.randint(-127, 128, (K, N), dtype=torch.int8, device=device,
+                          generator=torch.Generator(device=device).manual_seed(999))
+    else:  # w8a8: quantise N(0,1) fp32 sources with the library's own quantiser
+        import cudaintro_b200 as cb
+
+        x = torch.randn((M_local, K), device=device, generator=g)
+        a, rs = cb.quantize_absmax(x, 0)
+        del x
+        w = torch.randn((K, N), device=device, generator=torch.Generator(device=device).manual_seed(999))
+        b, cs = cb.quantize_absmax(w, 1)
+        del w
+        extra = {"row_scale": rs, "col_scale": cs}
+    return a, b, extra
+
+
+def out_dtype(kind):
+    import torch
+
+    return {"bf16": torch.bfloat16, "f16": torch.float16, "i8": torch.int32, "w8a8": torch.bfloat16}[kind]
+
+
+def launch(kind, a, b, c_slab, extra):
+    import cudaintro_b200 as cb
+
+    if kind == "bf16":
+        cb.gemm_bf16(a, b, out=c_slab)
+    elif kind == "f16":
+        cb.gemm_f16(a, b, out=c_slab)
+    elif kind == "i8":
+        cb.gemm_i8_i32(a, b, out=c_slab)
+    else:
+        cb.gemm_w8a8_bf16(a, b, extra["row_scale"], extra["col_scale"], out=c_slab)
+
+
+# ----------------------------------------------------------------------------- CPU legs
+
+def cpu_baseline_port(kind, M, N, K, target_seconds=10.0):
+    """The oracle (OpenMP restatement of the reference loop) on a bounded row sample of the workload."""
+    import numpy as np
+
+    import oracle as O
+
+    rng = np.random.default_rng(0)
+    threads = O.num_threads()
+
+    def run(rows):
+        idx = np.arange(rows, dtype=np.int64)
+        if kind in ("bf16", "f16"):
+            a = rng.standard_normal((rows, K)).astype(np.float32)
+            b = rng.standard_normal((K, N)).astype(np.float32)
+            if kind == "bf16":
+                ab, bb = O.f32_to_bf16_bits(a), O.f32_to_bf16_bits(b)
+            else:
+                ab, bb = a.astype(np.float16).view(np.uint16), b.astype(np.float16).view(np.uint16)
+            t0 = time.perf_counter()
+            O.gemm_h16(ab, bb, rows, N, K, kind == "bf16", O.ROW_MAJOR, idx)
+            return time.perf_counter() - t0
+        a = rng.integers(-127, 128, (rows, K)).astype(np.int8)
+        b = rng.integers(-127, 128, (K, N)).astype(np.int8)
+        if kind == "i8":
+            t0 = time.perf_counter()
+            O.gemm_i8_i32(a, b, rows, N, K, O.ROW_MAJOR, idx)
+            return time.perf_counter() - t0
+        rs = np.full(rows, 0.01, dtype=np.float32)
+        cs = np.full(N, 0.01, dtype=np.float32)
+        t0 = time.perf_counter()
+        O.gemm_w8a8_bf16(a, b, rs, cs, rows, N, K, idx)
+        return time.perf_counter() - t0
+
+    probe_rows = max(threads, 8)
+    t = run(probe_rows)
+    rows = int(min(M, max(probe_rows, probe_rows * target_seconds / max(t, 1e-3))))
+    rows = max(threads, rows // threads * threads)
+    t = run(rows)
+    ops = 2.0 * rows * N * K
+    return {"value": ops / t / 1e12, "unit": WORKLOADS_UNIT[kind], "cores": threads, "kind": "port",
+            "sample": f"{rows} of {M} rows of C (all N, all K) in {t:.2f} s; OpenMP restatement of the reference loop, "
+                      f"linear in rows: full problem would take {t * M / rows:.0f} s"}
+
+
+WORKLOADS_UNIT = {"bf16": "TFLOP/s", "f16": "TFLOP/s", "i8": "TOP/s", "w8a8": "TOP/s"}
+
+
+def reference_arm(args, wl_name):
+    """The reference's own CPU GEMM (matrixMulCPU, TileProgramming/tensor_utils.cu:35-45, built
+    unmodified into oracle/_ref/) on the host cores.  The function is square, fp32 and single
+    threaded, so a step runs T concurrent calls (one per host thread) on T distinct w x w x w
+    sub-blocks of the workload, with the workload's values widened to fp32."""
+    import numpy as np
+
+    import oracle as O
+
+    kind, M, N, K, _, _, unit = WORKLOADS[wl_name]
+    threads = os.cpu_count() or 1
+    have_ref = O.load_ref() is not None
+    w = 384
+    rng = np.random.default_rng(1)
+    blocks = []
+    for _ in range(threads):
+        if kind in ("bf16", "f16"):
+            a = rng.standard_normal((w, w)).astype(np.float32)
+            b = rng.standard_normal((w, w)).astype(np.float32)
+            if kind == "bf16":
+                a, b = O.bf16_bits_to_f32(O.f32_to_bf16_bits(a)), O.bf16_bits_to_f32(O.f32_to_bf16_bits(b))
+            else:
+                a, b = a.astype(np.float16).astype(np.float32), b.astype(np.float16).astype(np.float32)
+        else:
+            a = rng.integers(-127, 128, (w, w)).astype(np.float32)
+            b = rng.integers(-127, 128, (w, w)).astype(np.float32)
+        blocks.append((a, b))
+
+    def one(i):
+        a, b = blocks[i]
+        if have_ref:
+            O.ref_matrix_mul_cpu(a, b, w)
+        else:
+            O.gemm_f32(a, b, w, w, w)
+
+    def step():
+        if have_ref:
+            ts = [threading.Thread(target=one, args=(i,)) for i in range(threads)]
+            for t in ts:
+                t.start()
+            for t in ts:
+                t.join()
+        else:  # the port is already parallel inside
+            for i in range(threads):
+                one(i)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    ops = 2.0 * w ** 3 * threads * args.steps
+    value = ops / dt / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": {"bf16": "bf16", "f16": "f16", "i8": "int8", "w8a8": "int8"}[kind], "data": "synthetic",
+        "config": {"workload": wl_name, "M": M, "N": N, "K": K},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads,
+                         "kind": "reference" if have_ref else "port",
+                         "sample": f"each step = {threads} concurrent matrixMulCPU calls on distinct {w}^3 sub-blocks "
+                                   f"of the {M}x{N}x{K} problem (values widened to fp32)"},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- main
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="bf16_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-suite", action="store_true", help="skip the per-type side measurements")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            reference_arm(args, args.workload)
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    import cudaintro_b200 as cb
+    from cudaintro_b200 import capi
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the GEMM suite has no CPU path")
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    kind, M, N, K, in_b, out_b, unit = WORKLOADS[args.workload]
+    assert M % world == 0
+    M_local = M // world
+    a, b, extra = make_inputs(kind, M_local, N, K, device, seed=1234 + rank)
+    c_full = torch.empty((M, N), dtype=out_dtype(kind), device=device)
+    c_slab = c_full[rank * M_local:(rank + 1) * M_local]
+
+    def step():
+        launch(kind, a, b, c_slab, extra)
+        if world > 1:
+            dist.all_gather_into_tensor(c_full, c_slab)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    cb.check_device()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gemm_ms = 0.0
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    cb.check_device()
+
+    # kernel-only duration (no collective), measured live on the same stream right after
+    barrier()
+    g0.record()
+    for _ in range(args.steps):
+        launch(kind, a, b, c_slab, extra)
+    g1.record()
+    torch.cuda.synchronize()
+    gemm_ms = g0.elapsed_time(g1) / args.steps
+
+    t = torch.tensor([ms, gemm_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, gemm_ms = float(t[0]), float(t[1])
+
+    ops_step = 2.0 * M * N * K
+    value = ops_step * args.steps / (ms * 1e-3) / 1e12
+
+    # ---- end to end through the host-buffer C entry point (pinned memory, copies timed)
+    e2e = None
+    if kind != "w8a8":
+        code = {"bf16": capi.BF16, "f16": capi.F16, "i8": capi.I8}[kind]
+        ha = torch.empty((M_local, K), dtype=a.dtype).pin_memory()
+        hb = torch.empty((K, N), dtype=b.dtype).pin_memory()
+        hc = torch.empty((M_local, N), dtype=out_dtype(kind)).pin_memory()
+        ha.copy_(a)
+        hb.copy_(b)
+        e2e_steps = min(args.steps, 20)
+
+        def host_call():
+            st = capi.lib.b200_gemm_host(code, ha.data_ptr(), hb.data_ptr(), hc.data_ptr(), M_local, N, K, cb.ROW_MAJOR)
+            if st:
+                raise cb.B200Error(st, capi.lib.b200_last_error().decode())
+
+        for _ in range(3):
+            host_call()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            host_call()
+        dt = time.perf_counter() - t0
+        tt = torch.tensor([dt], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt[0])
+        e2e = {"value": ops_step * e2e_steps / dt / 1e12, "unit": unit,
+               "h2d_bytes_per_step": world * (M_local * K + K * N) * in_b, "d2h_bytes_per_step": M * N * out_b,
+               "steps": e2e_steps, "ms_per_step": dt / e2e_steps * 1e3,
+               "api": "b200_gemm_host (pinned host buffers; on N>1 each rank moves its A rows, B and its C rows)"}
+        capi.lib.b200_host_release()
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
+
+    peaks = measured_peaks()
+    timed_seconds = ms * 1e-3
+    peak_kind = "sustained" if timed_seconds > 2.0 else "burst"
+    scale = {"bf16": 1.0, "f16": 1.0, "i8": 2.0, "w8a8": 2.0}[kind]  # int8 runs at twice the bf16 rate
+    peak = peaks[peak_kind] * scale
+    gemm_ops = 2.0 * M_local * N * K
+    achieved = gemm_ops / (gemm_ms * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+        "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+        "kernel": "gemm_umma_kernel", "avg_launch_ms": gemm_ms,
+        "peak_source": f"{peaks['source']} cuBLAS bf16 {peak_kind}" + (" x2 for int8" if scale == 2.0 else ""),
+        "frac_of_nominal": achieved / NOMINAL_PEAK[kind],
+        "algorithmic_bytes_per_launch": (M_local * K + K * N) * in_b + M_local * N * out_b,
+    }
+
+    line = {
+        "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": {"bf16": "bf16", "f16": "f16", "i8": "int8", "w8a8": "int8"}[kind], "data": "synthetic",
+        "config": {"workload": args.workload, "M": M, "N": N, "K": K, "layout": "row-major",
+                   "parallelism": f"rows of A over {world} GPU(s), B replicated" + (", NCCL all-gather of C" if world > 1 else ""),
+                   "l2": "inputs larger than L2 (no flush needed)" if (M_local * K + K * N) * in_b > 126e6
+                         else "inputs fit L2: back-to-back launches re-use it"},
+        "roofline": roofline,
+        "clocks": clocks.summary(),
+        "gpu_launches": args.steps,
+        "frac_of_nominal_peak": value / world / NOMINAL_PEAK[kind],
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    if world > 1:
+        line["gemm_phase"] = {"ms": gemm_ms, "value": ops_step / (gemm_ms * 1e-3) / 1e12, "unit": unit,
+                              "note": "all ranks' GEMMs without the all-gather"}
+
+    if world == 1 and not args.no_suite:
+        line["suite"] = side_measurements(device, args.workload)
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline_port(kind, M, N, K)
+
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def side_measurements(device, main_workload):
+    """The other types of the metric at 8192^3 (and the W8A8 linear), each timed alone: best of 10
+    single launches.  Also the vendor library's GEMM on the same shapes as a yardstick."""
+    import torch
+
+    from cudaintro_b200 import capi
+
+    out = {}
+    for name in ("int8_8192", "bf16_8192", "fp16_8192", "w8a8"):
+        kind, M, N, K, _, _, unit = WORKLOADS[name]
+        a, b, extra = make_inputs(kind, M, N, K, device, seed=77)
+        c = torch.empty((M, N), dtype=out_dtype(kind), device=device)
+        what = {"bf16": capi.BF16, "f16": capi.F16, "i8": capi.I8, "w8a8": capi.W8A8}[kind]
+        for _ in range(3):
+            capi.time_gemm(what, a, b, c, M, N, K, iters=1, row_scale=extra.get("row_scale"), col_scale=extra.get("col_scale"))
+        best = min(capi.time_gemm(what, a, b, c, M, N, K, iters=1, row_scale=extra.get("row_scale"),
+                                  col_scale=extra.get("col_scale")) for _ in range(10))
+        val = 2.0 * M * N * K / (best * 1e-3) / 1e12
+        entry = {"value": val, "unit": unit, "ms": best, "frac_of_nominal_peak": val / NOMINAL_PEAK[kind]}
+        try:
+            if kind in ("bf16", "f16"):
+                fn = lambda: torch.matmul(a, b)  # noqa: E731
+            elif kind == "i8":
+                fn = lambda: torch._int_mm(a, b)  # noqa: E731
+            else:
+                fn = None
+            if fn is not None:
+                for _ in range(3):
+                    fn()
+                ts = []
+                for _ in range(10):
+                    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s.record()
+                    fn()
+                    e.record()
+                    torch.cuda.synchronize()
+                    ts.append(s.elapsed_time(e))
+                entry["vendor_library"] = {"value": 2.0 * M * N * K / (min(ts) * 1e-3) / 1e12, "ms": min(ts)}
+        except Exception as ex:
+            entry["vendor_library"] = {"error": repr(ex)[:120]}
+        out[name] = entry
+        del a, b, c, extra
+        torch.cuda.empty_cache()
+    return out
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,28 @@
+"""cudaintro_b200 — B200 (sm_100a) quantized GEMM suite behind a C ABI.
+
+The product is ``libb200gemm.so`` (``include/b200gemm.h``); this package loads it with ctypes
+and offers thin wrappers that take torch CUDA tensors, used by the tests and the bench.  Torch
+only provides device memory and streams here.  There is no CPU path: if the library cannot be
+loaded the import of :mod:`cudaintro_b200.capi` raises, and every call on a machine without a
+GPU returns an error status that the wrappers turn into :class:`B200Error`.
+"""
+from .capi import (  # noqa: F401
+    B200Error,
+    COL_MAJOR_NN,
+    F32_3XTF32,
+    F32_FFMA,
+    ROW_MAJOR,
+    ROW_MAJOR_BT,
+    check_device,
+    fill,
+    gemm_bf16,
+    gemm_f16,
+    gemm_f32,
+    gemm_host,
+    gemm_i8_i32,
+    gemm_naive,
+    gemm_w8a8_bf16,
+    lib,
+    quantize_absmax,
+    time_gemm,
+)

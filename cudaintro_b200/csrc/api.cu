@@ -1,0 +1,238 @@
+// The extern "C" surface of libb200gemm: argument checking, layout mapping and dispatch onto the
+// kernels.  Declarations and the reference call each entry point replaces: include/b200gemm.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "internal.h"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+static thread_local char g_last_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+namespace {
+
+int64_t packed_ld(int layout, char which, int64_t M, int64_t N, int64_t K) {
+  switch (layout) {
+    case B200_ROW_MAJOR: return which == 'a' ? K : N;               // A[M,K] B[K,N] C[M,N]
+    case B200_COL_MAJOR_NN: return which == 'a' ? M : (which == 'b' ? K : M);
+    case B200_ROW_MAJOR_BT: return which == 'a' ? K : (which == 'b' ? K : N);
+  }
+  return 0;
+}
+
+// Maps a problem in any of the three layouts onto the kernels' native form
+//   C'[M',N'] = A'[M',K] * B'   with A' K-contiguous, C' N'-contiguous,
+// B' either [K,N'] N'-contiguous or [N',K] K-contiguous.
+// Column-major C = A*B is the row-major product C^T = B^T * A^T: B (K contiguous per column)
+// becomes A', A (M contiguous per k) becomes B' in its [K,N'] form, and M and N trade places.
+struct Native {
+  const void* A;
+  const void* B;
+  int64_t M, N, K, lda, ldb, ldc;
+  bool b_is_nk;
+};
+
+int to_native(const void* A, const void* B, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+              int64_t ldc, int layout, Native* out) {
+  if (layout != B200_ROW_MAJOR && layout != B200_COL_MAJOR_NN && layout != B200_ROW_MAJOR_BT)
+    return fail(B200_ERR_BAD_ARGUMENT, "unknown layout %d", layout);
+  if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
+  if (lda == 0) lda = packed_ld(layout, 'a', M, N, K);
+  if (ldb == 0) ldb = packed_ld(layout, 'b', M, N, K);
+  if (ldc == 0) ldc = packed_ld(layout, 'c', M, N, K);
+  if (layout == B200_COL_MAJOR_NN) {
+    *out = Native{B, A, N, M, K, ldb, lda, ldc, false};
+  } else {
+    *out = Native{A, B, M, N, K, lda, ldb, ldc, layout == B200_ROW_MAJOR_BT};
+  }
+  return B200_OK;
+}
+
+int gemm_tensor(int kind, int epi, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                int64_t lda, int64_t ldb, int64_t ldc, int layout, const float* rs, const float* cs,
+                void* stream) {
+  Native nv;
+  int rc = to_native(A, B, M, N, K, lda, ldb, ldc, layout, &nv);
+  if (rc) return rc;
+  return launch_umma_gemm(kind, epi, nv.A, nv.B, C, nv.M, nv.N, nv.K, nv.lda, nv.ldb, nv.ldc, nv.b_is_nk, rs,
+                          cs, 0, static_cast<cudaStream_t>(stream));
+}
+
+// Device workspace of the *_host entry point (one per process, grows on demand).
+struct HostWorkspace {
+  std::mutex mu;
+  void* dA = nullptr;
+  void* dB = nullptr;
+  void* dC = nullptr;
+  size_t capA = 0, capB = 0, capC = 0;
+  cudaStream_t stream = nullptr;
+} g_ws;
+
+int grow(void** p, size_t* cap, size_t need) {
+  if (*cap >= need) return B200_OK;
+  if (*p) B200_CUDA_TRY(cudaFree(*p));
+  *p = nullptr;
+  *cap = 0;
+  B200_CUDA_TRY(cudaMalloc(p, need));
+  *cap = need;
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" const char* b200_last_error(void) { return g_last_error; }
+extern "C" const char* b200_version(void) { return "b200gemm 0.1 (sm_100a)"; }
+
+extern "C" int b200_sm_count(void) {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return n;
+}
+
+extern "C" int b200_check_device(void* stream) {
+  uint32_t st = 0;
+  int rc = read_and_clear_umma_status(static_cast<cudaStream_t>(stream), &st);
+  if (rc) return rc;
+  if (st) return fail(B200_ERR_DEVICE_WAIT, "a tensor-core kernel gave up a bounded wait (status 0x%x)", st);
+  return B200_OK;
+}
+
+extern "C" int b200_gemm_i8_i32(const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
+                                int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream) {
+  return gemm_tensor(KIND_I8, EPI_I32, A, B, C, M, N, K, lda, ldb, ldc, layout, nullptr, nullptr, stream);
+}
+extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                              int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream) {
+  return gemm_tensor(KIND_BF16, EPI_BF16, A, B, C, M, N, K, lda, ldb, ldc, layout, nullptr, nullptr, stream);
+}
+extern "C" int b200_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                             int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream) {
+  return gemm_tensor(KIND_F16, EPI_F16, A, B, C, M, N, K, lda, ldb, ldc, layout, nullptr, nullptr, stream);
+}
+extern "C" int b200_gemm_w8a8_bf16(const int8_t* A, const int8_t* B, const float* row_scale,
+                                   const float* col_scale, void* C, int64_t M, int64_t N, int64_t K,
+                                   int64_t lda, int64_t ldb, int64_t ldc, void* stream) {
+  return gemm_tensor(KIND_I8, EPI_W8A8_BF16, A, B, C, M, N, K, lda, ldb, ldc, B200_ROW_MAJOR, row_scale,
+                     col_scale, stream);
+}
+
+extern "C" int b200_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                             int64_t lda, int64_t ldb, int64_t ldc, int layout, int mode, void* stream) {
+  Native nv;
+  int rc = to_native(A, B, M, N, K, lda, ldb, ldc, layout, &nv);
+  if (rc) return rc;
+  if (mode == B200_F32_FFMA)
+    return launch_sgemm_ffma(static_cast<const float*>(nv.A), static_cast<const float*>(nv.B), C, nv.M, nv.N,
+                             nv.K, nv.lda, nv.ldb, nv.ldc, nv.b_is_nk, static_cast<cudaStream_t>(stream));
+  if (mode == B200_F32_3XTF32)
+    return launch_sgemm_3xtf32(static_cast<const float*>(nv.A), static_cast<const float*>(nv.B), C, nv.M, nv.N,
+                               nv.K, nv.lda, nv.ldb, nv.ldc, nv.b_is_nk, static_cast<cudaStream_t>(stream));
+  return fail(B200_ERR_BAD_ARGUMENT, "unknown fp32 mode %d", mode);
+}
+
+extern "C" int b200_gemm_naive(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N,
+                               int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream) {
+  if (layout != B200_ROW_MAJOR && layout != B200_COL_MAJOR_NN && layout != B200_ROW_MAJOR_BT)
+    return fail(B200_ERR_BAD_ARGUMENT, "unknown layout %d", layout);
+  if (lda == 0) lda = packed_ld(layout, 'a', M, N, K);
+  if (ldb == 0) ldb = packed_ld(layout, 'b', M, N, K);
+  if (ldc == 0) ldc = packed_ld(layout, 'c', M, N, K);
+  return launch_naive(dtype, A, B, C, M, N, K, lda, ldb, ldc, layout, static_cast<cudaStream_t>(stream));
+}
+
+static int dispatch(int what, const void* A, const void* B, void* C, const float* rs, const float* cs, int64_t M,
+                    int64_t N, int64_t K, int layout, int f32_mode, void* stream) {
+  switch (what) {
+    case B200_I8:
+      return b200_gemm_i8_i32(static_cast<const int8_t*>(A), static_cast<const int8_t*>(B),
+                              static_cast<int32_t*>(C), M, N, K, 0, 0, 0, layout, stream);
+    case B200_F16: return b200_gemm_f16(A, B, C, M, N, K, 0, 0, 0, layout, stream);
+    case B200_BF16: return b200_gemm_bf16(A, B, C, M, N, K, 0, 0, 0, layout, stream);
+    case B200_F32:
+      return b200_gemm_f32(static_cast<const float*>(A), static_cast<const float*>(B), static_cast<float*>(C), M,
+                           N, K, 0, 0, 0, layout, f32_mode, stream);
+    case B200_W8A8:
+      if (layout != B200_ROW_MAJOR) return fail(B200_ERR_BAD_ARGUMENT, "W8A8 is row-major only");
+      return b200_gemm_w8a8_bf16(static_cast<const int8_t*>(A), static_cast<const int8_t*>(B), rs, cs, C, M, N, K,
+                                 0, 0, 0, stream);
+  }
+  return fail(B200_ERR_BAD_ARGUMENT, "unknown dtype %d", what);
+}
+
+extern "C" int b200_time_gemm(int what, const void* A, const void* B, void* C, const float* row_scale,
+                              const float* col_scale, int64_t M, int64_t N, int64_t K, int layout, int f32_mode,
+                              int iters, float* ms, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!ms || iters <= 0) return fail(B200_ERR_BAD_ARGUMENT, "time_gemm: bad argument");
+  cudaEvent_t e0, e1;
+  B200_CUDA_TRY(cudaEventCreate(&e0));
+  B200_CUDA_TRY(cudaEventCreate(&e1));
+  int rc = B200_OK;
+  cudaEventRecord(e0, stream);
+  for (int i = 0; i < iters && rc == B200_OK; ++i)
+    rc = dispatch(what, A, B, C, row_scale, col_scale, M, N, K, layout, f32_mode, stream_);
+  cudaEventRecord(e1, stream);
+  cudaError_t se = cudaEventSynchronize(e1);
+  if (rc == B200_OK && se != cudaSuccess) rc = fail(B200_ERR_CUDA, "cudaEventSynchronize: %s", cudaGetErrorString(se));
+  if (rc == B200_OK) {
+    se = cudaEventElapsedTime(ms, e0, e1);
+    if (se != cudaSuccess) rc = fail(B200_ERR_CUDA, "cudaEventElapsedTime: %s", cudaGetErrorString(se));
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (rc == B200_OK) rc = b200_check_device(stream_);
+  return rc;
+}
+
+extern "C" int b200_gemm_host(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                              int layout) {
+  if (!A || !B || !C) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
+  size_t in_elem, out_elem;
+  switch (dtype) {
+    case B200_I8: in_elem = 1; out_elem = 4; break;
+    case B200_F16: case B200_BF16: in_elem = 2; out_elem = 2; break;
+    case B200_F32: in_elem = 4; out_elem = 4; break;
+    default: return fail(B200_ERR_BAD_ARGUMENT, "unknown dtype %d", dtype);
+  }
+  std::lock_guard<std::mutex> lock(g_ws.mu);
+  if (!g_ws.stream) B200_CUDA_TRY(cudaStreamCreateWithFlags(&g_ws.stream, cudaStreamNonBlocking));
+  const size_t bytesA = size_t(M) * K * in_elem, bytesB = size_t(K) * N * in_elem, bytesC = size_t(M) * N * out_elem;
+  int rc;
+  if ((rc = grow(&g_ws.dA, &g_ws.capA, bytesA))) return rc;
+  if ((rc = grow(&g_ws.dB, &g_ws.capB, bytesB))) return rc;
+  if ((rc = grow(&g_ws.dC, &g_ws.capC, bytesC))) return rc;
+  B200_CUDA_TRY(cudaMemcpyAsync(g_ws.dA, A, bytesA, cudaMemcpyHostToDevice, g_ws.stream));
+  B200_CUDA_TRY(cudaMemcpyAsync(g_ws.dB, B, bytesB, cudaMemcpyHostToDevice, g_ws.stream));
+  rc = dispatch(dtype, g_ws.dA, g_ws.dB, g_ws.dC, nullptr, nullptr, M, N, K, layout, B200_F32_FFMA, g_ws.stream);
+  if (rc) return rc;
+  B200_CUDA_TRY(cudaMemcpyAsync(C, g_ws.dC, bytesC, cudaMemcpyDeviceToHost, g_ws.stream));
+  return b200_check_device(g_ws.stream);
+}
+
+extern "C" int b200_host_release(void) {
+  std::lock_guard<std::mutex> lock(g_ws.mu);
+  if (g_ws.dA) cudaFree(g_ws.dA);
+  if (g_ws.dB) cudaFree(g_ws.dB);
+  if (g_ws.dC) cudaFree(g_ws.dC);
+  g_ws.dA = g_ws.dB = g_ws.dC = nullptr;
+  g_ws.capA = g_ws.capB = g_ws.capC = 0;
+  if (g_ws.stream) cudaStreamDestroy(g_ws.stream);
+  g_ws.stream = nullptr;
+  return B200_OK;
+}

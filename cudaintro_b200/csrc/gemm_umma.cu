@@ -1,0 +1,587 @@
+// Tensor-core GEMM for sm_100a: C[M,N] = A[M,K] * B, row-major, for int8 (int32 accumulate),
+// fp16 / bf16 and tf32 (fp32 accumulate).
+//
+// One persistent CTA per SM walks over 128 x BN output tiles.  Inside a CTA the work is split
+// by warp role:
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A tile
+//               (128 rows x 128 bytes of K) and the B tile into a ring of shared-memory stages,
+//               both with the 128-byte swizzle the MMA descriptors expect.
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (M = 128, N = BN, 32 bytes of K per
+//               instruction) from shared memory into an accumulator in tensor memory, and
+//               commits each stage back to the producer.  It also owns the TMEM allocation.
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (one output row per thread),
+//               convert / dequantise and store it with 16-byte stores.
+// The accumulator is double buffered in TMEM (2 x BN columns), so the epilogue of tile i
+// overlaps the main loop of tile i+1.
+//
+// B may be given either as [K,N] with N contiguous (the row-major product; also what the
+// reference's column-major cuBLAS call turns into once both sides are transposed) or as [N,K]
+// with K contiguous.  The first form is fed to the tensor cores as an "MN-major" operand: the
+// tile is loaded as BN*elem/128 column spans of 128 bytes, each BK rows tall.
+//
+// Every mbarrier wait is bounded; a wait that runs out raises a CTA-wide abort flag, all roles
+// drain, tensor memory is freed, and a status word tells the host that the result is invalid.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <mutex>
+
+#include "internal.h"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+__device__ uint32_t g_umma_status = 0;  // bit 0: a bounded wait ran out somewhere
+
+namespace {
+
+constexpr int BM = 128;          // rows of C per tile = TMEM lanes
+constexpr int kThreads = 192;    // producer warp, MMA warp, four epilogue warps
+constexpr int kSmemBudget = 227 * 1024;
+
+template <int KIND, int BN_>
+struct Tile {
+  static constexpr int ELEM = KIND == KIND_I8 ? 1 : (KIND == KIND_TF32 ? 4 : 2);
+  static constexpr int BN = BN_;
+  static constexpr int BK = 128 / ELEM;      // elements of K per stage (one 128-byte swizzle row)
+  static constexpr int UMMA_K = 32 / ELEM;   // elements of K per tcgen05.mma
+  static constexpr int SPAN = 128 / ELEM;    // elements of N in one 128-byte span (MN-major B)
+  static constexpr int NSPANS = BN / SPAN;
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int SPAN_BYTES = BK * 128;  // one span of B: BK k-rows of 128 bytes
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES_FIT = (kSmemBudget - 2048) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // BN is a power of two here
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+struct GemmArgs {
+  void* C;
+  int64_t ldc;
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int c_vec;  // 1 when C and ldc allow 16-byte stores
+  const float* row_scale;
+  const float* col_scale;
+};
+
+constexpr int kGroupM = 16;  // m-tiles that share a sweep over n (keeps A and B tiles hot in L2)
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
+  int per_group = kGroupM * tiles_n;
+  int g = t / per_group;
+  int first_m = g * kGroupM;
+  int gm = min(tiles_m - first_m, kGroupM);
+  int r = t - g * per_group;
+  mb = first_m + r % gm;
+  nb = r / gm;
+}
+
+template <int EPI>
+__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, const uint32_t (&v)[32],
+                                            float rs) {
+  // One thread owns row `row`, columns [n0, n0 + 32).
+  constexpr int OUT_BYTES = (EPI == EPI_I32 || EPI == EPI_F32) ? 4 : 2;
+  char* crow = static_cast<char*>(p.C) + (int64_t(row) * p.ldc + n0) * OUT_BYTES;
+  bool full = p.c_vec && n0 + 32 <= p.N;
+  if constexpr (EPI == EPI_I32 || EPI == EPI_F32) {
+    if (full) {
+      uint4* dst = reinterpret_cast<uint4*>(crow);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+      uint32_t* dst = reinterpret_cast<uint32_t*>(crow);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (n0 + i < p.N) dst[i] = v[i];
+    }
+  } else {
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float x0, x1;
+      if constexpr (EPI == EPI_W8A8_BF16) {
+        // (float(acc) * row_scale) * col_scale, each step rounded once, then to bf16
+        float c0 = __ldg(p.col_scale + min(n0 + 2 * i, p.N - 1));
+        float c1 = __ldg(p.col_scale + min(n0 + 2 * i + 1, p.N - 1));
+        x0 = __fmul_rn(__fmul_rn(__int2float_rn(int(v[2 * i])), rs), c0);
+        x1 = __fmul_rn(__fmul_rn(__int2float_rn(int(v[2 * i + 1])), rs), c1);
+      } else {
+        x0 = __uint_as_float(v[2 * i]);
+        x1 = __uint_as_float(v[2 * i + 1]);
+      }
+      if constexpr (EPI == EPI_F16) {
+        __half2 h = __floats2half2_rn(x0, x1);
+        packed[i] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+        packed[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    if (full) {
+      uint4* dst = reinterpret_cast<uint4*>(crow);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+    } else {
+      uint16_t* dst = reinterpret_cast<uint16_t*>(crow);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (n0 + i < p.N) dst[i] = uint16_t(packed[i >> 1] >> ((i & 1) * 16));
+    }
+  }
+}
+
+template <int KIND, int BN, bool B_NK, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmArgs p) {
+  using T = Tile<KIND, BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzle atoms are 1024 bytes: align the stage ring to that.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T::STAGES * T::STAGE_BYTES);
+  uint64_t* full_bar = bars;                   // [STAGES] producer -> MMA
+  uint64_t* empty_bar = bars + T::STAGES;      // [STAGES] MMA -> producer
+  uint64_t* acc_full = bars + 2 * T::STAGES;   // [2] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;          // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + T::BK - 1) / T::BK;
+  // Split-operand fp32 (3xTF32): A and B each arrive as two stacked planes, low parts on top of
+  // high parts, and K is walked three times: lo*hi, then hi*lo, then hi*hi (small terms first).
+  constexpr bool X3 = KIND == KIND_TF32;
+  const int total_kb = X3 ? 3 * num_kb : num_kb;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, T::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mb, nb;
+        tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        for (int kbt = 0; kbt < total_kb; ++kbt) {
+          const int pass = X3 ? kbt / num_kb : 0;
+          const int kb = kbt - pass * num_kb;
+          const int a_row0 = (X3 && pass != 0) ? p.M : 0;                       // plane 1 = high parts
+          const int b_row0 = (X3 && pass != 1) ? (B_NK ? p.N : p.K) : 0;
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * T::STAGE_BYTES;
+          uint8_t* sb = sa + T::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], T::STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * T::BK, a_row0 + mb * BM);
+          if constexpr (B_NK) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * T::BK, b_row0 + nb * BN);
+          } else {
+#pragma unroll
+            for (int s = 0; s < T::NSPANS; ++s)
+              tma_load_2d(sb + s * T::SPAN_BYTES, &tmap_b, &full_bar[stage], nb * BN + s * T::SPAN,
+                          b_row0 + kb * T::BK);
+          }
+          if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_instr_desc(KIND, BM, BN, 0, B_NK ? 0 : 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int ab = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait_bounded(&acc_empty[ab], acc_phase ^ 1u, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);
+        for (int kb = 0; kb < total_kb; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * T::STAGE_BYTES);
+          const uint32_t sb = sa + T::A_BYTES;
+          const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
+          // An N-contiguous operand of 32-bit elements only exists in the "128-byte swizzle on
+          // 32-byte chunks" form: atoms of 128 bytes of N by 4 k-rows (512 bytes).
+          const uint64_t b_desc = B_NK ? make_smem_desc_sw128(sb, 16, 1024)
+                                  : (KIND == KIND_TF32 ? make_smem_desc(sb, T::SPAN_BYTES, 512, 1)
+                                                       : make_smem_desc_sw128(sb, T::SPAN_BYTES, 1024));
+#pragma unroll
+          for (int j = 0; j < T::BK / T::UMMA_K; ++j) {
+            // A (and a K-contiguous B) advance 32 bytes inside the swizzle row; an N-contiguous
+            // B advances UMMA_K whole k-rows of 128 bytes.
+            const uint64_t a_adv = uint64_t((j * 32) >> 4);
+            const uint64_t b_adv = B_NK ? uint64_t((j * 32) >> 4) : uint64_t((j * T::UMMA_K * 128) >> 4);
+            umma<KIND>(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+          if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&acc_full[ab]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter + 32)
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      int mb, nb;
+      tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      const int ab = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait_bounded(&acc_full[ab], acc_phase, abort_flag)) break;
+      tc_fence_after_sync();
+      const int row = mb * BM + quarter * 32 + lane;
+      float rs = 0.f;
+      if constexpr (EPI == EPI_W8A8_BF16) rs = row < p.M ? __ldg(p.row_scale + row) : 0.f;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(ab * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int n0 = nb * BN + c * 32;
+        if (n0 >= p.N) break;  // uniform across the warp
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + uint32_t(c * 32), v);
+        tmem_ld_wait();
+        if (row < p.M) store_chunk<EPI>(p, row, n0, v, rs);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[ab]);
+    }
+  }
+
+  // Every role gets here: either its loop ended or its wait was abandoned.
+  __syncwarp();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicOr(&g_umma_status, 1u);
+    // Give copies and MMAs still in flight time to land before shared and tensor memory go away.
+    uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------ host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// 2-D tensor map over a row-major [rows, cols] matrix with leading dimension `ld` (elements):
+// box = box_cols x box_rows, 128-byte swizzle, zero fill outside the matrix.
+int make_map(CUtensorMap* map, int kind, const void* base, int64_t rows, int64_t cols, int64_t ld,
+             int box_cols, int box_rows, bool chunks32 = false) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  int elem = kind == KIND_I8 ? 1 : (kind == KIND_TF32 ? 4 : 2);
+  CUtensorMapDataType dt = kind == KIND_I8     ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                           : kind == KIND_F16  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                           : kind == KIND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(ld) * cuuint64_t(elem)};
+  cuuint32_t box[2] = {cuuint32_t(box_cols), cuuint32_t(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   chunks32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  return B200_OK;
+}
+
+int sm_count_of_current_device(int* out) {
+  static int cached[64] = {0};
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 64 && cached[dev]) { *out = cached[dev]; return B200_OK; }
+  int n = 0;
+  B200_CUDA_TRY(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+  if (dev < 64) cached[dev] = n;
+  *out = n;
+  return B200_OK;
+}
+
+template <int KIND, int BN, bool B_NK, int EPI>
+int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb,
+               cudaStream_t stream) {
+  using T = Tile<KIND, BN>;
+  auto kernel = gemm_umma_kernel<KIND, BN, B_NK, EPI>;
+  // The shared-memory attribute is per device: set it whenever this thread meets a new device.
+  static thread_local int last_dev = -1;
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev != last_dev) {
+    cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+    if (attr_err != cudaSuccess)
+      return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes of shared memory): %s", T::SMEM_BYTES,
+                  cudaGetErrorString(attr_err));
+    last_dev = dev;
+  }
+  CUtensorMap ma, mb;
+  constexpr int64_t planes = KIND == KIND_TF32 ? 2 : 1;  // split fp32 operands: low plane, then high plane
+  int rc = make_map(&ma, KIND, A, planes * args.M, args.K, lda, T::BK, BM);
+  if (rc) return rc;
+  if (B_NK)
+    rc = make_map(&mb, KIND, B, planes * args.N, args.K, ldb, T::BK, BN);
+  else
+    rc = make_map(&mb, KIND, B, planes * args.K, args.N, ldb, T::SPAN < BN ? T::SPAN : BN, T::BK,
+                  /*chunks32=*/KIND == KIND_TF32);
+  if (rc) return rc;
+  int sms = 0;
+  rc = sm_count_of_current_device(&sms);
+  if (rc) return rc;
+  int tiles = args.tiles_m * args.tiles_n;
+  int grid = tiles < sms ? tiles : sms;
+  kernel<<<grid, kThreads, T::SMEM_BYTES, stream>>>(ma, mb, args);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
+}
+
+template <int KIND, int BN, int EPI>
+int launch_major(bool b_nk, const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb,
+                 cudaStream_t stream) {
+  // An N-contiguous B is staged in whole 128-byte spans of N, so the tile cannot be narrower than one.
+  if constexpr (BN < Tile<KIND, BN>::SPAN) {
+    if (!b_nk) return fail(B200_ERR_BAD_ARGUMENT, "tile width %d is narrower than a 128-byte span", BN);
+    return launch_one<KIND, BN, true, EPI>(A, B, args, lda, ldb, stream);
+  } else {
+    return b_nk ? launch_one<KIND, BN, true, EPI>(A, B, args, lda, ldb, stream)
+                : launch_one<KIND, BN, false, EPI>(A, B, args, lda, ldb, stream);
+  }
+}
+
+template <int KIND, int EPI>
+int launch_bn(int bn, bool b_nk, const void* A, const void* B, GemmArgs args, int64_t lda, int64_t ldb,
+              cudaStream_t stream) {
+  args.tiles_n = int((args.N + bn - 1) / bn);
+  switch (bn) {
+    case 256: return launch_major<KIND, 256, EPI>(b_nk, A, B, args, lda, ldb, stream);
+    case 128: return launch_major<KIND, 128, EPI>(b_nk, A, B, args, lda, ldb, stream);
+    case 64: return launch_major<KIND, 64, EPI>(b_nk, A, B, args, lda, ldb, stream);
+  }
+  return fail(B200_ERR_BAD_ARGUMENT, "tile width %d is not built", bn);
+}
+
+}  // namespace
+
+int read_and_clear_umma_status(cudaStream_t stream, uint32_t* out) {
+  uint32_t zero = 0;
+  B200_CUDA_TRY(cudaStreamSynchronize(stream));
+  B200_CUDA_TRY(cudaMemcpyFromSymbol(out, g_umma_status, sizeof(uint32_t)));
+  if (*out) B200_CUDA_TRY(cudaMemcpyToSymbol(g_umma_status, &zero, sizeof(uint32_t)));
+  return B200_OK;
+}
+
+int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, int64_t M, int64_t N,
+                     int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
+                     const float* row_scale, const float* col_scale, int force_bn,
+                     cudaStream_t stream) {
+  if (!A || !B || !C) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
+  if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30))
+    return fail(B200_ERR_TOO_LARGE, "a dimension exceeds 2^30");
+  const int elem = kind == KIND_I8 ? 1 : (kind == KIND_TF32 ? 4 : 2);
+  const int out_elem = (epi == EPI_I32 || epi == EPI_F32) ? 4 : 2;
+  if (lda < K || ldb < (b_is_nk ? K : N) || ldc < N)
+    return fail(B200_ERR_BAD_ARGUMENT, "a leading dimension is smaller than the row it spans");
+  // A and B are read by TMA: 16-byte aligned base and row pitch.  C is written with plain
+  // stores: 16-byte vectors when its base and pitch allow, element by element otherwise.
+  if ((lda * elem) % 16 || (ldb * elem) % 16 || reinterpret_cast<uintptr_t>(A) % 16 ||
+      reinterpret_cast<uintptr_t>(B) % 16)
+    return fail(B200_ERR_UNSUPPORTED,
+                "tensor-core GEMM needs 16-byte aligned A and B pointers and leading dimensions "
+                "(lda=%lld ldb=%lld, element %d bytes)",
+                (long long)lda, (long long)ldb, elem);
+  if (reinterpret_cast<uintptr_t>(C) % out_elem)
+    return fail(B200_ERR_UNSUPPORTED, "C is not aligned to its element size");
+  if (epi == EPI_W8A8_BF16 && (!row_scale || !col_scale))
+    return fail(B200_ERR_BAD_ARGUMENT, "null scale pointer");
+
+  GemmArgs args;
+  args.C = C;
+  args.ldc = ldc;
+  args.M = int(M);
+  args.N = int(N);
+  args.K = int(K);
+  args.tiles_m = int((M + BM - 1) / BM);
+  args.tiles_n = 0;
+  args.c_vec = ((ldc * out_elem) % 16 == 0 && reinterpret_cast<uintptr_t>(C) % 16 == 0) ? 1 : 0;
+  args.row_scale = row_scale;
+  args.col_scale = col_scale;
+
+  int bn = force_bn;
+  if (bn == 0) {
+    int sms = 0;
+    int rc = sm_count_of_current_device(&sms);
+    if (rc) return rc;
+    // Widest tile that still gives every SM something to do.
+    bn = 256;
+    while (bn > 64 && int64_t(args.tiles_m) * ((N + bn - 1) / bn) < sms) bn >>= 1;
+  }
+  if (kind == KIND_I8 && !b_is_nk && bn < 128) bn = 128;  // an int8 span of N is 128 elements wide
+
+  switch (kind) {
+    case KIND_I8:
+      if (epi == EPI_I32) return launch_bn<KIND_I8, EPI_I32>(bn, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_W8A8_BF16)
+        return launch_bn<KIND_I8, EPI_W8A8_BF16>(bn, b_is_nk, A, B, args, lda, ldb, stream);
+      break;
+    case KIND_F16:
+      if (epi == EPI_F16) return launch_bn<KIND_F16, EPI_F16>(bn, b_is_nk, A, B, args, lda, ldb, stream);
+      break;
+    case KIND_BF16:
+      if (epi == EPI_BF16) return launch_bn<KIND_BF16, EPI_BF16>(bn, b_is_nk, A, B, args, lda, ldb, stream);
+      break;
+    case KIND_TF32:  // A and B are the stacked low/high planes made by launch_sgemm_3xtf32
+      if (epi == EPI_F32) return launch_bn<KIND_TF32, EPI_F32>(bn, b_is_nk, A, B, args, lda, ldb, stream);
+      break;
+    default:
+      break;
+  }
+  return fail(B200_ERR_BAD_ARGUMENT, "unsupported operand kind %d with epilogue %d", kind, epi);
+}
+
+// ------------------------------------------------------------------------------ 3xTF32
+namespace {
+
+__device__ __forceinline__ float round_to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// Splits a row-major [rows, cols] fp32 matrix into two tf32-exact planes stacked in `out`
+// ([2 * rows, ld_out]): plane 0 holds the low parts, plane 1 the high parts, x ~= hi + lo with
+// hi = tf32(x) and lo = tf32(x - hi).  Padding columns [cols, ld_out) are left untouched; the
+// tensor map that reads the planes stops at `cols`.
+__global__ void split_tf32_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t rows,
+                                  int64_t cols, int64_t ld_in, int64_t ld_out) {
+  const int64_t total = rows * cols;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const float v = x[r * ld_in + c];
+    const float hi = round_to_tf32(v);
+    const float lo = round_to_tf32(v - hi);
+    out[r * ld_out + c] = lo;
+    out[(rows + r) * ld_out + c] = hi;
+  }
+}
+
+// Per-device scratch for the split planes; grows on demand and is kept until the process ends.
+struct SplitScratch {
+  std::mutex mu;
+  float* buf[64] = {nullptr};
+  size_t cap[64] = {0};
+} g_split;
+
+}  // namespace
+
+int split_tf32_into(const float* A, const float* B, float* scratch, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, bool b_is_nk, int64_t* ld_a_out, int64_t* ld_b_out,
+                    float** planes_b, cudaStream_t stream) {
+  const int64_t a_cols = K, a_rows = M;
+  const int64_t b_cols = b_is_nk ? K : N, b_rows = b_is_nk ? N : K;
+  const int64_t lda_p = (a_cols + 3) & ~int64_t(3), ldb_p = (b_cols + 3) & ~int64_t(3);  // 16-byte rows
+  float* pa = scratch;
+  float* pb = scratch + 2 * a_rows * lda_p;
+  const int grid = 148 * 8;
+  split_tf32_kernel<<<grid, 256, 0, stream>>>(A, pa, a_rows, a_cols, lda, lda_p);
+  split_tf32_kernel<<<grid, 256, 0, stream>>>(B, pb, b_rows, b_cols, ldb, ldb_p);
+  B200_CUDA_TRY(cudaGetLastError());
+  *ld_a_out = lda_p;
+  *ld_b_out = ldb_p;
+  *planes_b = pb;
+  return B200_OK;
+}
+
+size_t split_tf32_scratch_floats(int64_t M, int64_t N, int64_t K, bool b_is_nk) {
+  const int64_t b_cols = b_is_nk ? K : N, b_rows = b_is_nk ? N : K;
+  return size_t(2 * M * ((K + 3) & ~int64_t(3)) + 2 * b_rows * ((b_cols + 3) & ~int64_t(3)));
+}
+
+int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                        int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream) {
+  if (!A || !B || !C) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
+  if (lda < K || ldb < (b_is_nk ? K : N) || ldc < N)
+    return fail(B200_ERR_BAD_ARGUMENT, "a leading dimension is smaller than the row it spans");
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 64) return fail(B200_ERR_UNSUPPORTED, "device ordinal %d is beyond the scratch table", dev);
+  const size_t need = split_tf32_scratch_floats(M, N, K, b_is_nk) * sizeof(float);
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_split.mu);
+    if (g_split.cap[dev] < need) {
+      if (g_split.buf[dev]) B200_CUDA_TRY(cudaFree(g_split.buf[dev]));  // waits for kernels still using it
+      g_split.buf[dev] = nullptr;
+      g_split.cap[dev] = 0;
+      B200_CUDA_TRY(cudaMalloc(&g_split.buf[dev], need));
+      g_split.cap[dev] = need;
+    }
+    scratch = g_split.buf[dev];
+  }
+  int64_t lda_p = 0, ldb_p = 0;
+  float* pb = nullptr;
+  int rc = split_tf32_into(A, B, scratch, M, N, K, lda, ldb, b_is_nk, &lda_p, &ldb_p, &pb, stream);
+  if (rc) return rc;
+  return launch_umma_gemm(KIND_TF32, EPI_F32, scratch, pb, C, M, N, K, lda_p, ldb_p, ldc, b_is_nk, nullptr,
+                          nullptr, 0, stream);
+}
+
+}  // namespace b200

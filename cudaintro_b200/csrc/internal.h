@@ -1,0 +1,44 @@
+// Declarations shared by the translation units of libb200gemm (not part of the public ABI).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200gemm.h"
+
+namespace b200 {
+
+// Records the text b200_last_error() returns on this thread and passes `code` through.
+int fail(int code, const char* fmt, ...);
+
+#define B200_CUDA_TRY(call)                                                          \
+  do {                                                                               \
+    cudaError_t e__ = (call);                                                        \
+    if (e__ != cudaSuccess)                                                          \
+      return ::b200::fail(B200_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e__)); \
+  } while (0)
+
+enum Epilogue { EPI_I32 = 0, EPI_F32 = 1, EPI_BF16 = 2, EPI_F16 = 3, EPI_W8A8_BF16 = 4 };
+
+// A row-major problem C[M,N] = A[M,K] * B with B either [K,N] (b_is_nk = false, N contiguous) or
+// [N,K] (b_is_nk = true, K contiguous), on the tensor cores.  `kind` is a b200::MmaKind value.
+// force_bn = 0 lets the launcher pick the tile width.
+int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, int64_t M, int64_t N,
+                     int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
+                     const float* row_scale, const float* col_scale, int force_bn,
+                     cudaStream_t stream);
+
+// Reads and clears the device-side wait record of the tensor-core kernels (0 = clean).
+int read_and_clear_umma_status(cudaStream_t stream, uint32_t* out);
+
+int launch_sgemm_ffma(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                      int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream);
+
+// 3xTF32: tensor-core fp32 GEMM from split operands (a = hi + lo, three products per term).
+int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                        int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream);
+
+int launch_naive(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                 int64_t lda, int64_t ldb, int64_t ldc, int layout, cudaStream_t stream);
+
+}  // namespace b200

@@ -1,0 +1,215 @@
+// Thin inline-PTX wrappers for the sm_100a features the GEMM kernels use: mbarriers, TMA tiled
+// loads, tensor memory (TMEM) allocation, tcgen05 MMA / commit / load, and the descriptors they
+// take.  Every wait in here is bounded: a wait that runs out returns false and the caller
+// records a status word instead of spinning for ever.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// ---------------------------------------------------------------------------- mbarrier
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Longest any single wait may last before the kernel gives up (a whole GEMM takes milliseconds).
+constexpr uint64_t kWaitBudgetNs = 4000000000ull;
+
+// Bounded wait on a phase of an mbarrier.  `abort_flag` is a shared-memory word that any role
+// of the CTA raises when its own wait ran out; every other role then leaves its wait too, so
+// that the CTA always reaches its final barrier and frees its tensor memory.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
+                                                  volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3ffu) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+        *abort_flag = 1u;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------- TMA
+
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+// 2-D tiled load global -> shared, completion counted in bytes on `bar`.  x is the innermost
+// (contiguous) coordinate in elements; x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x),
+        "r"(y)
+      : "memory");
+}
+
+// ---------------------------------------------------------------------------- tensor memory
+
+// Whole-warp calls (.sync.aligned).  `ncols` is a power of two in [32, 512].
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base lane + t).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// ---------------------------------------------------------------------------- tcgen05 MMA
+
+enum MmaKind { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2, KIND_TF32 = 3 };
+
+// 32-bit instruction descriptor of tcgen05.mma (dense, no negate, no saturate):
+//   [4,6) accumulator format 1 = f32, 2 = s32      [7,10) A format   [10,13) B format
+//   15 A major (0 = K contiguous, 1 = M contiguous) 16 B major (0 = K contiguous, 1 = N contiguous)
+//   [17,23) N >> 3      [24,29) M >> 4
+// Operand formats: kind::f16 0 = f16, 1 = bf16; kind::tf32 2; kind::i8 1 = signed.
+__host__ __device__ constexpr uint32_t make_instr_desc(int kind, int mma_m, int mma_n, int a_mn_major,
+                                                       int b_mn_major) {
+  uint32_t fmt = kind == KIND_F16 ? 0u : kind == KIND_BF16 ? 1u : kind == KIND_I8 ? 1u : 2u;
+  uint32_t cfmt = kind == KIND_I8 ? 2u : 1u;
+  return (cfmt << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(a_mn_major) << 15) |
+         (uint32_t(b_mn_major) << 16) | (uint32_t(mma_n >> 3) << 17) | (uint32_t(mma_m >> 4) << 24);
+}
+
+// 64-bit shared-memory operand descriptor, 128-byte swizzle (layout type 2), descriptor
+// version 1.  Offsets are in bytes here and stored divided by 16.
+//   K-contiguous operand : rows of 128 bytes, 8 rows form a 1024-byte swizzle atom;
+//                          stride_bytes = distance between 8-row groups; leading_bytes unused.
+//   MN-contiguous operand: 128 bytes of M/N by 8 k-rows form the atom;
+//                          leading_bytes = distance between successive 128-byte spans of M/N,
+//                          stride_bytes  = distance between successive groups of 8 k-rows.
+//   Layout type 1 is the 128-byte swizzle applied to 32-byte chunks (atoms of 128 bytes of M/N by
+//   4 k-rows), the only form an MN-contiguous operand of 32-bit elements can take; it pairs with
+//   the tensor-map swizzle CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t leading_bytes,
+                                                   uint32_t stride_bytes, uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr & 0x3ffffu) >> 4);
+  d |= uint64_t((leading_bytes >> 4) & 0x3fffu) << 16;
+  d |= uint64_t((stride_bytes >> 4) & 0x3fffu) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(layout_type) << 61;
+  return d;
+}
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t leading_bytes,
+                                                         uint32_t stride_bytes) {
+  return make_smem_desc(smem_addr, leading_bytes, stride_bytes, 2);
+}
+
+template <int KIND>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                     uint32_t accumulate) {
+  if constexpr (KIND == KIND_I8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else if constexpr (KIND == KIND_TF32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+// Makes `bar` receive one arrival once every MMA this thread issued so far has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+
+}  // namespace b200

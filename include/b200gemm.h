@@ -1,0 +1,134 @@
+/*
+ * b200gemm — C ABI of the B200 (sm_100a) quantized GEMM suite.
+ *
+ * These entry points stand where the reference calls cublasGemmEx inside its per-type benchmark
+ * bodies; each one cites the call it replaces (paths are inside the reference project).
+ * All matrix pointers are DEVICE pointers unless the name ends in _host.  Every call is
+ * asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the default stream) and
+ * returns a b200_status; nothing here exits the process or traps the GPU.  There is no CPU
+ * route: without a usable sm_100 device the calls return B200_ERR_CUDA.
+ *
+ * Layouts
+ *   B200_ROW_MAJOR     C[m*ldc+n] = sum_k A[m*lda+k] * B[k*ldb+n]
+ *   B200_COL_MAJOR_NN  C[m+n*ldc] = sum_k A[m+k*lda] * B[k+n*ldb]   (what the reference passes to
+ *                      cuBLAS: CUBLAS_OP_N, CUBLAS_OP_N, lda = M, ldb = K, ldc = M)
+ *   B200_ROW_MAJOR_BT  C[m*ldc+n] = sum_k A[m*lda+k] * B[n*ldb+k]   (B stored transposed, [N,K])
+ * A leading dimension of 0 means "packed" (the natural one for the layout).
+ *
+ * Tensor-core entry points (int8, fp16, bf16, W8A8) read A and B with TMA: lda and ldb, times
+ * the element size, must be multiples of 16 bytes and both base pointers 16-byte aligned;
+ * otherwise they return B200_ERR_UNSUPPORTED.  C has no such rule (an unaligned C is written
+ * element by element).  M, N and K themselves may be any positive sizes.
+ */
+#ifndef B200GEMM_H_
+#define B200GEMM_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b200_status {
+  B200_OK = 0,
+  B200_ERR_BAD_ARGUMENT = 1, /* null pointer, non-positive size, unknown enum value          */
+  B200_ERR_UNSUPPORTED = 2,  /* alignment or leading-dimension rule above not met            */
+  B200_ERR_CUDA = 3,         /* a CUDA runtime / driver call failed (see b200_last_error)    */
+  B200_ERR_DEVICE_WAIT = 4,  /* a kernel gave up a bounded wait; results are not valid       */
+  B200_ERR_TOO_LARGE = 5     /* size beyond a stated maximum of the entry point              */
+} b200_status;
+
+typedef enum b200_layout {
+  B200_ROW_MAJOR = 0,
+  B200_COL_MAJOR_NN = 1,
+  B200_ROW_MAJOR_BT = 2
+} b200_layout;
+
+typedef enum b200_f32_mode {
+  B200_F32_FFMA = 0,  /* fp32 FMA on the CUDA cores, k ascending                              */
+  B200_F32_3XTF32 = 1 /* three tf32 tensor-core products per term (hi*hi + hi*lo + lo*hi)     */
+} b200_f32_mode;
+
+/* Text of the most recent failure on the calling thread ("" if none). */
+const char* b200_last_error(void);
+
+/* Library / device facts: version string, SM count of the current device (0 if none). */
+const char* b200_version(void);
+int b200_sm_count(void);
+
+/* Waits for `stream` and reports whether any kernel of this library gave up a device-side wait
+ * since the last call (B200_ERR_DEVICE_WAIT), clearing the record. */
+int b200_check_device(void* stream);
+
+/* int8 x int8 -> int32, exact.  Replaces cublasGemmEx(CUDA_R_8I, CUDA_R_8I, CUDA_R_32I,
+ * CUBLAS_COMPUTE_32I) at quantization/GEMM_int8.cu:51-56 and :64-69. */
+int b200_gemm_i8_i32(const int8_t* A, const int8_t* B, int32_t* C, int64_t M, int64_t N, int64_t K,
+                     int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream);
+
+/* bf16 x bf16, fp32 accumulate, bf16 out (round to nearest even).  Replaces
+ * cublasGemmEx(CUDA_R_16BF ..., CUBLAS_COMPUTE_32F) at quantization/GEMM_bf16.cu:51-56, :64-69. */
+int b200_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                   int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream);
+
+/* fp16 x fp16, fp32 accumulate, fp16 out.  Replaces cublasGemmEx(CUDA_R_16F ...,
+ * CUBLAS_COMPUTE_32F) at quantization/GEMM_fp16.cu:51-56, :64-69. */
+int b200_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                  int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream);
+
+/* fp32 GEMM.  Replaces cublasGemmEx(CUDA_R_32F ..., CUBLAS_COMPUTE_32F) at
+ * quantization/GEMM_fp32.cu:49-54, :62-67, and the tiled kernel launched at
+ * TileProgramming/kernel.cu:145-147.  `mode` is a b200_f32_mode. No alignment rule in FFMA mode. */
+int b200_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                  int64_t lda, int64_t ldb, int64_t ldc, int layout, int mode, void* stream);
+
+/* W8A8 linear (row-major only): int8 x int8 -> int32 exactly, then
+ *   C[m][n] = bf16_rn( ((float)acc * row_scale[m]) * col_scale[n] ).
+ * row_scale has M entries, col_scale N entries (fp32, device).  A per-tensor scale is a
+ * row_scale/col_scale filled with one value.  No counterpart in the reference (its int8 body,
+ * quantization/GEMM_int8.cu:21-91, stops at the int32 result); this is the dequantising
+ * epilogue fused onto that same product. */
+int b200_gemm_w8a8_bf16(const int8_t* A, const int8_t* B, const float* row_scale,
+                        const float* col_scale, void* C, int64_t M, int64_t N, int64_t K,
+                        int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
+/* Symmetric absmax quantiser of a row-major fp32 [R, C] matrix to int8 (same shape):
+ *   along = 0: scale[r] = max_c |x[r][c]| / 127  (R scales);  along = 1: per column (C scales);
+ *   q = clamp(rint(x / scale), -127, 127), ties to even; an all-zero row/column gets scale 1.
+ * No counterpart in the reference; it makes the inputs of b200_gemm_w8a8_bf16. */
+int b200_quantize_absmax(const float* x, int8_t* q, float* scale, int64_t R, int64_t C, int along,
+                         void* stream);
+
+/* The reference's input generators (quantization/GEMM_int8.cu:8-19, GEMM_fp16.cu:8-19,
+ * GEMM_bf16.cu:8-19, GEMM_fp32.cu:7-17): element i = hash(i ^ seed) mapped to [lo, hi]. */
+int b200_fill_int8(int8_t* data, int64_t count, uint64_t seed, int lo, int hi, void* stream);
+int b200_fill_f16(void* data, int64_t count, uint64_t seed, float lo, float hi, void* stream);
+int b200_fill_bf16(void* data, int64_t count, uint64_t seed, float lo, float hi, void* stream);
+int b200_fill_f32(float* data, int64_t count, uint64_t seed, float lo, float hi, void* stream);
+
+/* Validation kernels: one thread per element of C, k ascending, no tensor cores, no tiling.
+ * `dtype` is a b200_dtype; out is int32 for B200_I8, fp32 sums (not rounded) for the others.
+ * They exist so that a full-size result of the fast kernels can be compared on the device. */
+typedef enum b200_dtype { B200_I8 = 0, B200_F16 = 1, B200_BF16 = 2, B200_F32 = 3 } b200_dtype;
+int b200_gemm_naive(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream);
+
+/* Same products with HOST buffers: copies A and B to the device, runs the kernel, copies C
+ * back, and returns after the result is in `C`.  `dtype` selects the entry point above
+ * (B200_I8 -> int32 out, B200_F16 / B200_BF16 -> 16-bit out, B200_F32 -> FFMA).  Device
+ * workspace is kept between calls and grows as needed; b200_host_release() frees it. */
+int b200_gemm_host(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                   int layout);
+int b200_host_release(void);
+
+/* Timing helper used by the legacy suite bodies and the bench: runs `iters` back-to-back
+ * launches of one of the GEMMs above on `stream` between two CUDA events and returns the
+ * elapsed milliseconds in *ms.  row_scale/col_scale are only read for B200_W8A8. */
+#define B200_W8A8 4
+int b200_time_gemm(int dtype_or_w8a8, const void* A, const void* B, void* C, const float* row_scale,
+                   const float* col_scale, int64_t M, int64_t N, int64_t K, int layout, int f32_mode,
+                   int iters, float* ms, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200GEMM_H_ */

@@ -1,0 +1,94 @@
+"""CPU tests of the drop-in boundary: the library builds, loads, and exports every symbol its
+headers declare; argument errors are reported as status codes without touching a GPU."""
+import ctypes as C
+import os
+import re
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b200gemm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_all_bound_and_exported(cb):
+    from cudaintro_b200 import capi
+
+    names = declared_symbols()
+    assert len(names) >= 15
+    assert set(names) == set(capi.SIGNATURES), "capi.SIGNATURES must list exactly the header's entry points"
+    handle = C.CDLL(capi.LIB_PATH)
+    for n in names:
+        assert getattr(handle, n) is not None
+
+
+def test_reference_suite_symbols_are_exported(cb):
+    """The mangled names the reference's main.cu links against (quantization/gemm_common.h:64-67)."""
+    from cudaintro_b200 import capi
+
+    out = subprocess.run(["nm", "-D", "--defined-only", capi.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    for dt in ("bf16", "fp16", "fp32", "int8"):
+        assert f"_Z13run_gemm_{dt}P13cublasContext" in out
+
+
+def test_gemm_result_layout_matches_reference_record(tmp_path):
+    """GemmResult is {const char*, uint64_t, double, double}: 32 bytes, fields at 0/8/16/24."""
+    src = tmp_path / "t.cpp"
+    src.write_text(
+        '#include "gemm_common.h"\n#include <cstddef>\n#include <cstdio>\n'
+        'int main(){std::printf("%zu %zu %zu %zu %zu",sizeof(GemmResult),offsetof(GemmResult,name),'
+        "offsetof(GemmResult,iters),offsetof(GemmResult,secs),offsetof(GemmResult,tflops));}\n")
+    exe = tmp_path / "t"
+    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    assert subprocess.run([str(exe)], capture_output=True, text=True).stdout.split() == ["32", "0", "8", "16", "24"]
+
+
+def test_bad_arguments_are_status_codes_not_crashes(cb):
+    from cudaintro_b200 import capi
+
+    lib = capi.lib
+    one = C.c_void_p(16)
+    # null pointers / non-positive sizes / unknown enums are rejected before any CUDA call
+    assert lib.b200_gemm_i8_i32(None, None, None, 128, 128, 128, 0, 0, 0, 0, None) == 1
+    assert b"null" in lib.b200_last_error()
+    assert lib.b200_gemm_i8_i32(one, one, one, 0, 128, 128, 0, 0, 0, 0, None) == 1
+    assert lib.b200_gemm_bf16(one, one, one, 128, 128, 128, 0, 0, 0, 7, None) == 1
+    assert lib.b200_gemm_f32(one, one, one, 8, 8, 8, 0, 0, 0, 0, 9, None) == 1
+    assert lib.b200_quantize_absmax(one, one, one, 4, 4, 2, None) == 1
+    assert lib.b200_gemm_naive(11, one, one, one, 4, 4, 4, 0, 0, 0, 0, None) == 1
+    # alignment rule of the tensor-core entry points: K = 100 int8 elements is not a 16-byte row
+    assert lib.b200_gemm_i8_i32(one, one, one, 128, 128, 100, 0, 0, 0, 0, None) == 2
+    assert b"16-byte" in lib.b200_last_error()
+    assert lib.b200_gemm_bf16(C.c_void_p(8), one, one, 128, 128, 128, 0, 0, 0, 0, None) == 2  # misaligned A
+    # leading dimension smaller than the row
+    assert lib.b200_gemm_f16(one, one, one, 64, 64, 64, 32, 0, 0, 0, None) == 1
+
+
+def test_no_cpu_fallback_without_device(cb):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("this check is for machines without a GPU")
+    from cudaintro_b200 import capi
+
+    one = C.c_void_p(16)
+    assert capi.lib.b200_sm_count() == 0
+    st = capi.lib.b200_gemm_i8_i32(one, one, one, 128, 128, 128, 0, 0, 0, 0, None)
+    assert st == 3, "without a device the call must fail with B200_ERR_CUDA, never compute on the CPU"
+
+
+def test_product_does_not_reference_the_oracle():
+    """The shipped package must not import or link the oracle (it is test infrastructure)."""
+    pkg = os.path.join(ROOT, "cudaintro_b200")
+    for dirpath, _, files in os.walk(pkg):
+        if os.path.basename(dirpath) == "build":
+            continue
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "liboracle" not in text and "import oracle" not in text and "from oracle" not in text, f
