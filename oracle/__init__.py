@@ -33,6 +33,8 @@ def build(ref_tree: str | None = None) -> None:
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
     if ref_tree and os.path.isdir(os.path.join(ref_tree, "TileProgramming")):
         subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={ref_tree}"], check=True)
+        if os.path.exists(os.path.join(os.path.dirname(HERE), "cudaintro_b200", "libb200gemm.so")):
+            subprocess.run(["make", "-s", "-C", HERE, "suite", f"REF={ref_tree}"], check=True)
 
 
 def load() -> C.CDLL:
