@@ -24,6 +24,7 @@ SIGNATURES = {
     "b200_last_error": (C.c_char_p, []),
     "b200_version": (C.c_char_p, []),
     "b200_sm_count": (_int, []),
+    "b200_set_tile_policy": (_int, [_int, _int]),
     "b200_check_device": (_int, [_p]),
     "b200_gemm_i8_i32": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
     "b200_gemm_bf16": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
@@ -203,6 +204,11 @@ def fill(t, seed: int, lo=None, hi=None):
                   torch.float32: lib.b200_fill_f32}[t.dtype]
             _check(fn(t.data_ptr(), n, seed, -1.0 if lo is None else lo, 1.0 if hi is None else hi, _stream()))
     return t
+
+
+def set_tile_policy(cta_group: int = 0, tile_n: int = 0) -> None:
+    """Forces single CTAs (1) or CTA pairs (2) and a tile width; zeros restore the automatic choice."""
+    _check(lib.b200_set_tile_policy(cta_group, tile_n))
 
 
 def check_device() -> None:

@@ -104,6 +104,8 @@ extern "C" int b200_sm_count(void) {
   return n;
 }
 
+extern "C" int b200_set_tile_policy(int cta_group, int tile_n) { return set_tile_policy(cta_group, tile_n); }
+
 extern "C" int b200_check_device(void* stream) {
   uint32_t st = 0;
   int rc = read_and_clear_umma_status(static_cast<cudaStream_t>(stream), &st);

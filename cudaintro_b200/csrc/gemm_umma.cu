@@ -40,16 +40,21 @@ constexpr int BM = 128;          // rows of C per tile = TMEM lanes
 constexpr int kThreads = 192;    // producer warp, MMA warp, four epilogue warps
 constexpr int kSmemBudget = 227 * 1024;
 
-template <int KIND, int BN_>
+// CG = 1: one CTA owns a 128 x BN tile.  CG = 2: a pair of CTAs (cluster of 2) owns a 256 x BN tile;
+// each CTA stages its own 128 rows of A and its own BN/2 columns of B, and the even-ranked CTA
+// issues tcgen05.mma.cta_group::2 for both.
+template <int KIND, int BN_, int CG_ = 1>
 struct Tile {
   static constexpr int ELEM = KIND == KIND_I8 ? 1 : (KIND == KIND_TF32 ? 4 : 2);
   static constexpr int BN = BN_;
+  static constexpr int CG = CG_;
+  static constexpr int BN_CTA = BN / CG;     // B columns staged by one CTA
   static constexpr int BK = 128 / ELEM;      // elements of K per stage (one 128-byte swizzle row)
   static constexpr int UMMA_K = 32 / ELEM;   // elements of K per tcgen05.mma
   static constexpr int SPAN = 128 / ELEM;    // elements of N in one 128-byte span (MN-major B)
-  static constexpr int NSPANS = BN / SPAN;
+  static constexpr int NSPANS = BN_CTA / SPAN;
   static constexpr int A_BYTES = BM * 128;
-  static constexpr int B_BYTES = BN * 128;
+  static constexpr int B_BYTES = BN_CTA * 128;
   static constexpr int SPAN_BYTES = BK * 128;  // one span of B: BK k-rows of 128 bytes
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES_FIT = (kSmemBudget - 2048) / STAGE_BYTES;
@@ -135,24 +140,28 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, 
   }
 }
 
-template <int KIND, int BN, bool B_NK, int EPI>
+template <int KIND, int BN, bool B_NK, int EPI, int CG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmArgs p) {
-  using T = Tile<KIND, BN>;
+  using T = Tile<KIND, BN, CG>;
+  constexpr int TILE_M = BM * CG;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes: align the stage ring to that.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T::STAGES * T::STAGE_BYTES);
-  uint64_t* full_bar = bars;                   // [STAGES] producer -> MMA
-  uint64_t* empty_bar = bars + T::STAGES;      // [STAGES] MMA -> producer
-  uint64_t* acc_full = bars + 2 * T::STAGES;   // [2] MMA -> epilogue
-  uint64_t* acc_empty = acc_full + 2;          // [2] epilogue -> MMA
+  uint64_t* full_bar = bars;                   // [STAGES] producer(s) -> MMA   (pair: the leader's is used)
+  uint64_t* empty_bar = bars + T::STAGES;      // [STAGES] MMA -> producer      (pair: one in each CTA)
+  uint64_t* acc_full = bars + 2 * T::STAGES;   // [2] MMA -> epilogue           (pair: one in each CTA)
+  uint64_t* acc_empty = acc_full + 2;          // [2] epilogue -> MMA           (pair: the leader's is used)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = CG == 2 ? cluster_cta_rank() : 0u;  // 0 = leader of the pair
+  const int first_tile = CG == 2 ? int(blockIdx.x >> 1) : int(blockIdx.x);
+  const int tile_step = CG == 2 ? int(gridDim.x >> 1) : int(gridDim.x);
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_kb = (p.K + T::BK - 1) / T::BK;
   // Split-operand fp32 (3xTF32): A and B each arrive as two stacked planes, low parts on top of
@@ -167,7 +176,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], 4 * CG);  // one arrival per epilogue warp (of both CTAs of a pair)
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -175,11 +184,16 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, T::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (CG == 2) {
+      tmem_alloc_pair(tmem_slot, T::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, T::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -189,9 +203,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
         int mb, nb;
         tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        const int m0 = mb * TILE_M + int(cta_rank) * BM;
+        const int n0 = nb * BN + int(cta_rank) * T::BN_CTA;
         for (int kbt = 0; kbt < total_kb; ++kbt) {
           const int pass = X3 ? kbt / num_kb : 0;
           const int kb = kbt - pass * num_kb;
@@ -200,29 +216,51 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * T::STAGE_BYTES;
           uint8_t* sb = sa + T::A_BYTES;
-          mbar_arrive_expect_tx(&full_bar[stage], T::STAGE_BYTES);
-          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * T::BK, a_row0 + mb * BM);
-          if constexpr (B_NK) {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * T::BK, b_row0 + nb * BN);
-          } else {
+          if constexpr (CG == 2) {
+            // Both CTAs' bytes are credited to the leader's barrier; only the leader arms it.
+            const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * T::STAGE_BYTES);
+            tma_load_2d_pair(sa, &tmap_a, bar, kb * T::BK, a_row0 + m0);
+            if constexpr (B_NK) {
+              tma_load_2d_pair(sb, &tmap_b, bar, kb * T::BK, b_row0 + n0);
+            } else {
 #pragma unroll
-            for (int s = 0; s < T::NSPANS; ++s)
-              tma_load_2d(sb + s * T::SPAN_BYTES, &tmap_b, &full_bar[stage], nb * BN + s * T::SPAN,
-                          b_row0 + kb * T::BK);
+              for (int s = 0; s < T::NSPANS; ++s)
+                tma_load_2d_pair(sb + s * T::SPAN_BYTES, &tmap_b, bar, n0 + s * T::SPAN, b_row0 + kb * T::BK);
+            }
+          } else {
+            mbar_arrive_expect_tx(&full_bar[stage], T::STAGE_BYTES);
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * T::BK, a_row0 + m0);
+            if constexpr (B_NK) {
+              tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * T::BK, b_row0 + n0);
+            } else {
+#pragma unroll
+              for (int s = 0; s < T::NSPANS; ++s)
+                tma_load_2d(sb + s * T::SPAN_BYTES, &tmap_b, &full_bar[stage], n0 + s * T::SPAN,
+                            b_row0 + kb * T::BK);
+            }
           }
+          if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if constexpr (CG == 2) {
+        // Stay until every stage this CTA filled has been released: the releases are arrivals sent
+        // by the leader's MMA commits into this CTA's shared memory, which must still exist.
+        for (int i = 0; i < T::STAGES && ok; ++i) {
+          ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag);
           if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_instr_desc(KIND, BM, BN, 0, B_NK ? 0 : 1);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_instr_desc(KIND, TILE_M, BN, 0, B_NK ? 0 : 1);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
         const int ab = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait_bounded(&acc_empty[ab], acc_phase ^ 1u, abort_flag)) break;
@@ -245,26 +283,32 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // B advances UMMA_K whole k-rows of 128 bytes.
             const uint64_t a_adv = uint64_t((j * 32) >> 4);
             const uint64_t b_adv = B_NK ? uint64_t((j * 32) >> 4) : uint64_t((j * T::UMMA_K * 128) >> 4);
-            umma<KIND>(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, (kb | j) != 0 ? 1u : 0u);
+            if constexpr (CG == 2)
+              umma_pair<KIND>(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, (kb | j) != 0 ? 1u : 0u);
+            else
+              umma<KIND>(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, (kb | j) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+          // the stage is free (in both CTAs of a pair) once these MMAs have read it
+          if constexpr (CG == 2) umma_commit_pair(&empty_bar[stage], 3); else umma_commit(&empty_bar[stage]);
           if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit(&acc_full[ab]);
+        if (ok) {
+          if constexpr (CG == 2) umma_commit_pair(&acc_full[ab], 3); else umma_commit(&acc_full[ab]);
+        }
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter + 32)
     int it = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+    for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mb, nb;
       tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
       const int ab = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait_bounded(&acc_full[ab], acc_phase, abort_flag)) break;
       tc_fence_after_sync();
-      const int row = mb * BM + quarter * 32 + lane;
+      const int row = mb * TILE_M + int(cta_rank) * BM + quarter * 32 + lane;
       float rs = 0.f;
       if constexpr (EPI == EPI_W8A8_BF16) rs = row < p.M ? __ldg(p.row_scale + row) : 0.f;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(ab * BN);
@@ -279,7 +323,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[ab]);
+      if (lane == 0) {
+        if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[ab]), 0));
+        else mbar_arrive(&acc_empty[ab]);
+      }
     }
   }
 
@@ -293,10 +340,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, T::TMEM_COLS);
+    if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, T::TMEM_COLS); else tmem_dealloc(tmem_base, T::TMEM_COLS);
   }
 }
 
@@ -355,11 +402,11 @@ int sm_count_of_current_device(int* out) {
   return B200_OK;
 }
 
-template <int KIND, int BN, bool B_NK, int EPI>
+template <int KIND, int BN, bool B_NK, int EPI, int CG>
 int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb,
                cudaStream_t stream) {
-  using T = Tile<KIND, BN>;
-  auto kernel = gemm_umma_kernel<KIND, BN, B_NK, EPI>;
+  using T = Tile<KIND, BN, CG>;
+  auto kernel = gemm_umma_kernel<KIND, BN, B_NK, EPI, CG>;
   // The shared-memory attribute is per device: set it whenever this thread meets a new device.
   static thread_local int last_dev = -1;
   int dev = 0;
@@ -376,47 +423,81 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
   int rc = make_map(&ma, KIND, A, planes * args.M, args.K, lda, T::BK, BM);
   if (rc) return rc;
   if (B_NK)
-    rc = make_map(&mb, KIND, B, planes * args.N, args.K, ldb, T::BK, BN);
+    rc = make_map(&mb, KIND, B, planes * args.N, args.K, ldb, T::BK, T::BN_CTA);
   else
-    rc = make_map(&mb, KIND, B, planes * args.K, args.N, ldb, T::SPAN < BN ? T::SPAN : BN, T::BK,
+    rc = make_map(&mb, KIND, B, planes * args.K, args.N, ldb, T::SPAN < T::BN_CTA ? T::SPAN : T::BN_CTA, T::BK,
                   /*chunks32=*/KIND == KIND_TF32);
   if (rc) return rc;
   int sms = 0;
   rc = sm_count_of_current_device(&sms);
   if (rc) return rc;
   int tiles = args.tiles_m * args.tiles_n;
-  int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, kThreads, T::SMEM_BYTES, stream>>>(ma, mb, args);
-  B200_CUDA_TRY(cudaGetLastError());
+  if constexpr (CG == 2) {
+    int pairs = tiles < sms / 2 ? tiles : sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(2 * pairs));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = T::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ma, mb, args));
+  } else {
+    int grid = tiles < sms ? tiles : sms;
+    kernel<<<grid, kThreads, T::SMEM_BYTES, stream>>>(ma, mb, args);
+    B200_CUDA_TRY(cudaGetLastError());
+  }
   return B200_OK;
 }
 
-template <int KIND, int BN, int EPI>
+template <int KIND, int BN, int EPI, int CG>
 int launch_major(bool b_nk, const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb,
                  cudaStream_t stream) {
-  // An N-contiguous B is staged in whole 128-byte spans of N, so the tile cannot be narrower than one.
-  if constexpr (BN < Tile<KIND, BN>::SPAN) {
-    if (!b_nk) return fail(B200_ERR_BAD_ARGUMENT, "tile width %d is narrower than a 128-byte span", BN);
-    return launch_one<KIND, BN, true, EPI>(A, B, args, lda, ldb, stream);
+  // An N-contiguous B is staged in whole 128-byte spans of N, so a CTA's share of the tile cannot be
+  // narrower than one span.
+  if constexpr (BN / CG < Tile<KIND, BN, CG>::SPAN) {
+    if (!b_nk) return fail(B200_ERR_BAD_ARGUMENT, "tile width %d is narrower than a 128-byte span", BN / CG);
+    return launch_one<KIND, BN, true, EPI, CG>(A, B, args, lda, ldb, stream);
   } else {
-    return b_nk ? launch_one<KIND, BN, true, EPI>(A, B, args, lda, ldb, stream)
-                : launch_one<KIND, BN, false, EPI>(A, B, args, lda, ldb, stream);
+    return b_nk ? launch_one<KIND, BN, true, EPI, CG>(A, B, args, lda, ldb, stream)
+                : launch_one<KIND, BN, false, EPI, CG>(A, B, args, lda, ldb, stream);
   }
 }
 
 template <int KIND, int EPI>
-int launch_bn(int bn, bool b_nk, const void* A, const void* B, GemmArgs args, int64_t lda, int64_t ldb,
+int launch_bn(int bn, int cg, bool b_nk, const void* A, const void* B, GemmArgs args, int64_t lda, int64_t ldb,
               cudaStream_t stream) {
   args.tiles_n = int((args.N + bn - 1) / bn);
+  args.tiles_m = int((args.M + BM * cg - 1) / (BM * cg));
+  if (cg == 2) {
+    if (bn == 256) return launch_major<KIND, 256, EPI, 2>(b_nk, A, B, args, lda, ldb, stream);
+    return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs are built for 256-wide tiles only");
+  }
   switch (bn) {
-    case 256: return launch_major<KIND, 256, EPI>(b_nk, A, B, args, lda, ldb, stream);
-    case 128: return launch_major<KIND, 128, EPI>(b_nk, A, B, args, lda, ldb, stream);
-    case 64: return launch_major<KIND, 64, EPI>(b_nk, A, B, args, lda, ldb, stream);
+    case 256: return launch_major<KIND, 256, EPI, 1>(b_nk, A, B, args, lda, ldb, stream);
+    case 128: return launch_major<KIND, 128, EPI, 1>(b_nk, A, B, args, lda, ldb, stream);
+    case 64: return launch_major<KIND, 64, EPI, 1>(b_nk, A, B, args, lda, ldb, stream);
   }
   return fail(B200_ERR_BAD_ARGUMENT, "tile width %d is not built", bn);
 }
 
+int g_force_cg = 0, g_force_bn = 0;  // 0 = automatic; set through b200_set_tile_policy
+
 }  // namespace
+
+int set_tile_policy(int cg, int bn) {
+  if ((cg != 0 && cg != 1 && cg != 2) || (bn != 0 && bn != 64 && bn != 128 && bn != 256))
+    return fail(B200_ERR_BAD_ARGUMENT, "tile policy: cta group must be 0, 1 or 2 and width 0, 64, 128 or 256");
+  if (cg == 2 && bn != 0 && bn != 256) return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs need 256-wide tiles");
+  g_force_cg = cg;
+  g_force_bn = bn;
+  return B200_OK;
+}
 
 int read_and_clear_umma_status(cudaStream_t stream, uint32_t* out) {
   uint32_t zero = 0;
@@ -463,11 +544,18 @@ int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, i
   args.row_scale = row_scale;
   args.col_scale = col_scale;
 
-  int bn = force_bn;
+  int sms = 0;
+  int rc = sm_count_of_current_device(&sms);
+  if (rc) return rc;
+  int bn = force_bn ? force_bn : g_force_bn;
+  int cg = g_force_cg;
+  if (cg == 0) {
+    // CTA pairs (256 x 256 tiles) once they give every pair of SMs a tile; single CTAs below that.
+    const int64_t pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    cg = (bn == 0 || bn == 256) && pair_tiles >= sms / 2 ? 2 : 1;
+  }
+  if (cg == 2) bn = 256;
   if (bn == 0) {
-    int sms = 0;
-    int rc = sm_count_of_current_device(&sms);
-    if (rc) return rc;
     // Widest tile that still gives every SM something to do.
     bn = 256;
     while (bn > 64 && int64_t(args.tiles_m) * ((N + bn - 1) / bn) < sms) bn >>= 1;
@@ -476,18 +564,18 @@ int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, i
 
   switch (kind) {
     case KIND_I8:
-      if (epi == EPI_I32) return launch_bn<KIND_I8, EPI_I32>(bn, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_I32) return launch_bn<KIND_I8, EPI_I32>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
       if (epi == EPI_W8A8_BF16)
-        return launch_bn<KIND_I8, EPI_W8A8_BF16>(bn, b_is_nk, A, B, args, lda, ldb, stream);
+        return launch_bn<KIND_I8, EPI_W8A8_BF16>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
       break;
     case KIND_F16:
-      if (epi == EPI_F16) return launch_bn<KIND_F16, EPI_F16>(bn, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_F16) return launch_bn<KIND_F16, EPI_F16>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
       break;
     case KIND_BF16:
-      if (epi == EPI_BF16) return launch_bn<KIND_BF16, EPI_BF16>(bn, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_BF16) return launch_bn<KIND_BF16, EPI_BF16>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
       break;
     case KIND_TF32:  // A and B are the stacked low/high planes made by launch_sgemm_3xtf32
-      if (epi == EPI_F32) return launch_bn<KIND_TF32, EPI_F32>(bn, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_F32) return launch_bn<KIND_TF32, EPI_F32>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
       break;
     default:
       break;

@@ -28,6 +28,9 @@ int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, i
                      const float* row_scale, const float* col_scale, int force_bn,
                      cudaStream_t stream);
 
+// Overrides the automatic choice of CTA grouping (1 or 2 CTAs per tile) and tile width; 0 = automatic.
+int set_tile_policy(int cg, int bn);
+
 // Reads and clears the device-side wait record of the tensor-core kernels (0 = clean).
 int read_and_clear_umma_status(cudaStream_t stream, uint32_t* out);
 

@@ -56,6 +56,12 @@ const char* b200_last_error(void);
 const char* b200_version(void);
 int b200_sm_count(void);
 
+/* Tuning knob for tests and measurements (process-wide, not thread-safe against running calls):
+ * forces the tensor-core kernels to use single CTAs (cta_group = 1) or CTA pairs (2) per tile
+ * and a tile width of 64, 128 or 256 columns; 0 restores the automatic choice.  CTA pairs exist
+ * for 256-wide tiles only.  Results do not depend on the policy. */
+int b200_set_tile_policy(int cta_group, int tile_n);
+
 /* Waits for `stream` and reports whether any kernel of this library gave up a device-side wait
  * since the last call (B200_ERR_DEVICE_WAIT), clearing the record. */
 int b200_check_device(void* stream);

@@ -472,3 +472,72 @@ def test_suite_entry_points_keep_the_reference_protocol(cb, device, monkeypatch)
         assert r.iters >= 256 and r.iters % 256 == 0
         assert r.secs >= 0.2
         assert abs(r.tflops - 2.0 * 4096 ** 3 * r.iters / (r.secs * 1e12)) <= 1e-9 * r.tflops
+
+
+# ------------------------------------------------------------------ tile policies (single CTAs vs CTA pairs)
+
+@pytest.fixture
+def policy(cb):
+    yield cb.set_tile_policy
+    cb.set_tile_policy(0, 0)
+
+
+POLICY_SHAPES = [(256, 256, 128), (208, 336, 1008), (16, 512, 4112), (1024, 768, 2048), (257, 272, 64)]
+
+
+@pytest.mark.parametrize("cg,bn", [(1, 256), (1, 128), (2, 256)])
+@pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "COL_MAJOR_NN", "ROW_MAJOR_BT"])
+@pytest.mark.parametrize("shape", POLICY_SHAPES)
+def test_int8_every_tile_policy_is_bit_exact(cb, oracle, device, policy, shape, layout_name, cg, bn):
+    layout = getattr(cb, layout_name)
+    M, N, K = shape
+    if layout == cb.COL_MAJOR_NN and M % 16:
+        M = (M + 15) // 16 * 16
+    rng = np.random.default_rng(hash((M, N, K, layout, cg, bn)) & 0xFFFF)
+    sa, sb = storage_shapes(cb, M, N, K, layout)
+    a = rng.integers(-127, 128, sa).astype(np.int8)
+    b = rng.integers(-127, 128, sb).astype(np.int8)
+    policy(cg, bn)
+    c = cb.gemm_i8_i32(to_dev(a, device), to_dev(b, device), layout)
+    cb.check_device()
+    assert np.array_equal(c.cpu().numpy(), oracle_i8(oracle, cb, a, b, M, N, K, layout))
+
+
+@pytest.mark.parametrize("cg,bn", [(1, 256), (1, 64), (2, 256)])
+@pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "ROW_MAJOR_BT"])
+def test_16bit_and_tf32_every_tile_policy(cb, oracle, device, policy, layout_name, cg, bn):
+    import torch
+
+    layout = getattr(cb, layout_name)
+    M, N, K = 392, 520, 1032
+    rng = np.random.default_rng(cg * 1000 + bn + layout)
+    sa, sb = storage_shapes(cb, M, N, K, layout)
+    af = rng.standard_normal(sa).astype(np.float32)
+    bf = rng.standard_normal(sb).astype(np.float32)
+    policy(cg, bn)
+    a16, b16 = oracle.f32_to_bf16_bits(af), oracle.f32_to_bf16_bits(bf)
+    c = cb.gemm_bf16(to_dev(a16.view(np.int16), device, torch.bfloat16), to_dev(b16.view(np.int16), device, torch.bfloat16),
+                     layout)
+    cb.check_device()
+    b_kn = b16 if layout == cb.ROW_MAJOR else np.ascontiguousarray(b16.T)
+    _, o32 = oracle.gemm_h16(a16, b_kn, M, N, K, True)
+    assert rel_fro(c.float().cpu().numpy(), o32) <= TOL_BF16
+    c32 = cb.gemm_f32(to_dev(af, device), to_dev(bf, device), layout, mode=cb.F32_3XTF32)
+    cb.check_device()
+    bf_kn = bf if layout == cb.ROW_MAJOR else np.ascontiguousarray(bf.T)
+    assert rel_fro(c32.cpu().numpy(), oracle.gemm_f32(af, bf_kn, M, N, K, acc64=True)) <= TOL_F32
+
+
+def test_w8a8_tile_policies_agree_bit_for_bit(cb, oracle, device, policy):
+    import torch
+
+    M, N, K = 520, 784, 2048
+    rng = np.random.default_rng(77)
+    qx, sx = oracle.quantize_absmax(rng.standard_normal((M, K)).astype(np.float32), 0)
+    qw, sw = oracle.quantize_absmax(rng.standard_normal((K, N)).astype(np.float32), 1)
+    want = oracle.gemm_w8a8_bf16(qx, qw, sx, sw, M, N, K)
+    for cg, bn in ((1, 256), (1, 128), (2, 256)):
+        policy(cg, bn)
+        c = cb.gemm_w8a8_bf16(to_dev(qx, device), to_dev(qw, device), to_dev(sx, device), to_dev(sw, device))
+        cb.check_device()
+        assert np.array_equal(c.view(torch.int16).cpu().numpy().view(np.uint16), want), (cg, bn)
