@@ -24,7 +24,7 @@ SIGNATURES = {
     "b200_last_error": (C.c_char_p, []),
     "b200_version": (C.c_char_p, []),
     "b200_sm_count": (_int, []),
-    "b200_set_tile_policy": (_int, [_int, _int]),
+    "b200_set_tile_policy": (_int, [_int, _int, _int]),
     "b200_check_device": (_int, [_p]),
     "b200_gemm_i8_i32": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
     "b200_gemm_bf16": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
@@ -206,9 +206,10 @@ def fill(t, seed: int, lo=None, hi=None):
     return t
 
 
-def set_tile_policy(cta_group: int = 0, tile_n: int = 0) -> None:
-    """Forces single CTAs (1) or CTA pairs (2) and a tile width; zeros restore the automatic choice."""
-    _check(lib.b200_set_tile_policy(cta_group, tile_n))
+def set_tile_policy(cta_group: int = 0, tile_n: int = 0, group_rows: int = 0) -> None:
+    """Forces single CTAs (1) or CTA pairs (2), a tile width and the rows per tile-order group;
+    zeros restore the automatic choice."""
+    _check(lib.b200_set_tile_policy(cta_group, tile_n, group_rows))
 
 
 def check_device() -> None:

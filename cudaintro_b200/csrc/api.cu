@@ -104,7 +104,9 @@ extern "C" int b200_sm_count(void) {
   return n;
 }
 
-extern "C" int b200_set_tile_policy(int cta_group, int tile_n) { return set_tile_policy(cta_group, tile_n); }
+extern "C" int b200_set_tile_policy(int cta_group, int tile_n, int group_rows) {
+  return set_tile_policy(cta_group, tile_n, group_rows);
+}
 
 extern "C" int b200_check_device(void* stream) {
   uint32_t st = 0;

@@ -68,14 +68,18 @@ struct GemmArgs {
   int64_t ldc;
   int M, N, K;
   int tiles_m, tiles_n;
+  int group_m;  // m-tiles per group of the tile order
   int c_vec;  // 1 when C and ldc allow 16-byte stores
   const float* row_scale;
   const float* col_scale;
 };
 
-constexpr int kGroupM = 16;  // m-tiles that share a sweep over n (keeps A and B tiles hot in L2)
+constexpr int kDefaultGroupRows = 4096;  // rows of C that share a sweep over n (keeps their A slab hot in L2)
 
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
+// Tile order: groups of kGroupRows rows; inside a group m runs fastest, then n.  A wave of
+// concurrently running tiles is then a near-square patch of C, which needs the fewest operand bytes,
+// and successive waves of a group re-use the group's slab of A.
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int kGroupM, int& mb, int& nb) {
   int per_group = kGroupM * tiles_n;
   int g = t / per_group;
   int first_m = g * kGroupM;
@@ -203,14 +207,19 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+      int it = 0;
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
         int mb, nb;
-        tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+        // Every other tile walks K backwards: a tile then starts on the k-blocks its predecessor
+        // touched last, which are the ones still in L2 (a forward-only sweep over a slab larger
+        // than the cache would evict each block just before it is needed again).
+        const bool k_reversed = (it & 1) != 0;
         const int m0 = mb * TILE_M + int(cta_rank) * BM;
         const int n0 = nb * BN + int(cta_rank) * T::BN_CTA;
         for (int kbt = 0; kbt < total_kb; ++kbt) {
           const int pass = X3 ? kbt / num_kb : 0;
-          const int kb = kbt - pass * num_kb;
+          const int kb = k_reversed ? num_kb - 1 - (kbt - pass * num_kb) : kbt - pass * num_kb;
           const int a_row0 = (X3 && pass != 0) ? p.M : 0;                       // plane 1 = high parts
           const int b_row0 = (X3 && pass != 1) ? (B_NK ? p.N : p.K) : 0;
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -303,7 +312,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int it = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mb, nb;
-      tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+      tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
       const int ab = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait_bounded(&acc_full[ab], acc_phase, abort_flag)) break;
@@ -469,11 +478,15 @@ int launch_major(bool b_nk, const void* A, const void* B, const GemmArgs& args, 
   }
 }
 
+int g_force_cg = 0, g_force_bn = 0, g_group_rows = 0;  // 0 = automatic; set through b200_set_tile_policy
+
 template <int KIND, int EPI>
 int launch_bn(int bn, int cg, bool b_nk, const void* A, const void* B, GemmArgs args, int64_t lda, int64_t ldb,
               cudaStream_t stream) {
   args.tiles_n = int((args.N + bn - 1) / bn);
   args.tiles_m = int((args.M + BM * cg - 1) / (BM * cg));
+  args.group_m = (g_group_rows ? g_group_rows : kDefaultGroupRows) / (BM * cg);
+  if (args.group_m < 1) args.group_m = 1;
   if (cg == 2) {
     if (bn == 256) return launch_major<KIND, 256, EPI, 2>(b_nk, A, B, args, lda, ldb, stream);
     return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs are built for 256-wide tiles only");
@@ -486,16 +499,17 @@ int launch_bn(int bn, int cg, bool b_nk, const void* A, const void* B, GemmArgs 
   return fail(B200_ERR_BAD_ARGUMENT, "tile width %d is not built", bn);
 }
 
-int g_force_cg = 0, g_force_bn = 0;  // 0 = automatic; set through b200_set_tile_policy
-
 }  // namespace
 
-int set_tile_policy(int cg, int bn) {
+int set_tile_policy(int cg, int bn, int group_rows) {
+  if (group_rows < 0 || (group_rows % 256) != 0)
+    return fail(B200_ERR_BAD_ARGUMENT, "tile policy: group rows must be a non-negative multiple of 256");
   if ((cg != 0 && cg != 1 && cg != 2) || (bn != 0 && bn != 64 && bn != 128 && bn != 256))
     return fail(B200_ERR_BAD_ARGUMENT, "tile policy: cta group must be 0, 1 or 2 and width 0, 64, 128 or 256");
   if (cg == 2 && bn != 0 && bn != 256) return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs need 256-wide tiles");
   g_force_cg = cg;
   g_force_bn = bn;
+  g_group_rows = group_rows;
   return B200_OK;
 }
 

@@ -29,7 +29,7 @@ int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, i
                      cudaStream_t stream);
 
 // Overrides the automatic choice of CTA grouping (1 or 2 CTAs per tile) and tile width; 0 = automatic.
-int set_tile_policy(int cg, int bn);
+int set_tile_policy(int cg, int bn, int group_rows);
 
 // Reads and clears the device-side wait record of the tensor-core kernels (0 = clean).
 int read_and_clear_umma_status(cudaStream_t stream, uint32_t* out);

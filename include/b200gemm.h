@@ -58,9 +58,11 @@ int b200_sm_count(void);
 
 /* Tuning knob for tests and measurements (process-wide, not thread-safe against running calls):
  * forces the tensor-core kernels to use single CTAs (cta_group = 1) or CTA pairs (2) per tile
- * and a tile width of 64, 128 or 256 columns; 0 restores the automatic choice.  CTA pairs exist
- * for 256-wide tiles only.  Results do not depend on the policy. */
-int b200_set_tile_policy(int cta_group, int tile_n);
+ * and a tile width of 64, 128 or 256 columns; `group_rows` (a multiple of 256) is how many rows
+ * of C share one sweep across N in the tile order.  0 restores the automatic choice of each.
+ * CTA pairs exist for 256-wide tiles only.  Integer results do not depend on the policy;
+ * floating-point results may differ in the last bits (the order of the K blocks changes). */
+int b200_set_tile_policy(int cta_group, int tile_n, int group_rows);
 
 /* Waits for `stream` and reports whether any kernel of this library gave up a device-side wait
  * since the last call (B200_ERR_DEVICE_WAIT), clearing the record. */
