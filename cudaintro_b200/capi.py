@@ -30,6 +30,7 @@ SIGNATURES = {
     "b200_gemm_bf16": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
     "b200_gemm_f16": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
     "b200_gemm_f32": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _p]),
+    "b200_gemm_f32_3xtf32_static": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
     "b200_gemm_w8a8_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p]),
     "b200_quantize_absmax": (_int, [_p, _p, _p, _i64, _i64, _int, _p]),
     "b200_fill_int8": (_int, [_p, _i64, C.c_uint64, _int, _int, _p]),

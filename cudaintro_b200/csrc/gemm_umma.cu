@@ -687,3 +687,85 @@ int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int
 }
 
 }  // namespace b200
+
+// ------------------------------------------------------------------------------ 3xTF32 without allocation
+//
+// Some hosts cannot let a plug-in allocate device memory: an inference server that handed the
+// whole GPU to its own memory pool at start-up and treats any later cudaMalloc as a bug, or a
+// control loop with a hard latency bound, where the implicit device-wide synchronisation of
+// cudaMalloc / cudaFree (and the chance of it failing for lack of memory) is not acceptable.
+// For them the split planes of the 3xTF32 GEMM live in a fixed array that is part of the
+// library image: every GPU that loads the library carries it until the process ends.
+namespace b200 {
+namespace {
+
+constexpr size_t kStaticSplitFloats = size_t(8) << 20;  // 8 Mi floats = 32 MiB per device
+
+static __device__ __align__(256) float g_static_split[kStaticSplitFloats];
+
+// Device address of g_static_split on each device, looked up once per device.  In host code the
+// array's name is only a handle for the runtime, not an address a kernel could use.
+std::mutex g_static_mu;
+float* g_static_ptr[64] = {nullptr};
+
+int static_split_address(float** out) {
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200_ERR_UNSUPPORTED, "device ordinal %d is beyond the scratch table", dev);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_split);  // for the device that is current now
+    if (e != cudaSuccess)
+      return fail(B200_ERR_CUDA, "cudaGetSymbolAddress(static scratch) on device %d: %s", dev, cudaGetErrorString(e));
+    g_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_gemm_f32_3xtf32_static(const float* A, const float* B, float* C, int64_t M, int64_t N,
+                                           int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int layout,
+                                           void* stream_) {
+  using namespace b200;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!A || !B || !C) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
+  if (layout != B200_ROW_MAJOR && layout != B200_COL_MAJOR_NN && layout != B200_ROW_MAJOR_BT)
+    return fail(B200_ERR_BAD_ARGUMENT, "unknown layout %d", layout);
+  // Same mapping onto the kernels' row-major form as the allocating entry point: a column-major
+  // product is the row-major product of the swapped operands.
+  const float* a = A;
+  const float* b = B;
+  int64_t m = M, n = N;
+  bool b_is_nk = layout == B200_ROW_MAJOR_BT;
+  if (lda == 0) lda = layout == B200_COL_MAJOR_NN ? M : K;
+  if (ldb == 0) ldb = layout == B200_ROW_MAJOR ? N : K;
+  if (ldc == 0) ldc = layout == B200_COL_MAJOR_NN ? M : N;
+  if (layout == B200_COL_MAJOR_NN) {
+    a = B; b = A; m = N; n = M;
+    int64_t t = lda; lda = ldb; ldb = t;
+  }
+  if (lda < K || ldb < (b_is_nk ? K : n) || ldc < n)
+    return fail(B200_ERR_BAD_ARGUMENT, "a leading dimension is smaller than the row it spans");
+  const size_t need = split_tf32_scratch_floats(m, n, K, b_is_nk);
+  if (need > kStaticSplitFloats)
+    return fail(B200_ERR_TOO_LARGE,
+                "the split planes of this %lld x %lld x %lld product need %zu floats; the built-in scratch "
+                "holds %zu (2*M*K + 2*K*N, rows padded to 4 floats, must not exceed it)",
+                (long long)M, (long long)N, (long long)K, need, kStaticSplitFloats);
+  float* scratch = nullptr;
+  int rc = static_split_address(&scratch);
+  if (rc) return rc;
+  // Every word of the scratch that the GEMM reads is rewritten by the split below, so nothing left
+  // over from an earlier call has to be cleared.
+  int64_t lda_p = 0, ldb_p = 0;
+  float* pb = nullptr;
+  rc = split_tf32_into(a, b, scratch, m, n, K, lda, ldb, b_is_nk, &lda_p, &ldb_p, &pb, stream);
+  if (rc) return rc;
+  return launch_umma_gemm(KIND_TF32, EPI_F32, scratch, pb, C, m, n, K, lda_p, ldb_p, ldc, b_is_nk, nullptr, nullptr,
+                          0, stream);
+}

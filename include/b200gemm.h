@@ -89,6 +89,26 @@ int b200_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, i
 int b200_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                   int64_t lda, int64_t ldb, int64_t ldc, int layout, int mode, void* stream);
 
+/* The 3xTF32 product of b200_gemm_f32 for callers that must not allocate device memory.
+ * No counterpart in the reference.  b200_gemm_f32 in 3xTF32 mode keeps the split (high / low)
+ * copies of A and B in a workspace it obtains with cudaMalloc and grows on demand; this variant
+ * keeps them in a fixed 32 MiB array built into the library instead, and calls neither
+ * cudaMalloc nor cudaFree nor anything else that allocates.  It is meant for hosts that gave
+ * all device memory to a pool of their own and forbid plug-ins to allocate, and for loops with
+ * a latency bound that the device-wide synchronisation inside cudaMalloc / cudaFree would break.
+ *   - Limit: 2*M*K + 2*K*N floats (each row padded to a multiple of 4 floats) must fit in
+ *     8 Mi floats, e.g. up to 1024 x 1024 x 2048; larger products return B200_ERR_TOO_LARGE.
+ *   - Every GPU that loads the library holds the 32 MiB until the process exits.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before any stream
+ *     capture begins.
+ *   - All calls on a device share the one array.  Each call rewrites every word it later reads,
+ *     so nothing has to be cleared between calls, but two calls whose kernels overlap on the GPU
+ *     (different streams, or different host threads) race on it: serialise them.
+ * Arguments, layouts, result and error codes are those of b200_gemm_f32. */
+int b200_gemm_f32_3xtf32_static(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                                int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream);
+
 /* W8A8 linear (row-major only): int8 x int8 -> int32 exactly, then
  *   C[m][n] = bf16_rn( ((float)acc * row_scale[m]) * col_scale[n] ).
  * row_scale has M entries, col_scale N entries (fp32, device).  A per-tensor scale is a
