@@ -300,6 +300,9 @@ def main():
     ap.add_argument("--no-suite", action="store_true", help="skip the per-type side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N>1: fused = the GEMM epilogue stores each tile into every rank's C over NVLink; "
+                         "nccl = GEMM, then NCCL all-gather")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -327,21 +330,38 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     kind, M, N, K, in_b, out_b, unit = WORKLOADS[args.workload]
-    assert M % world == 0
-    M_local = M // world
-    a, b, extra = make_inputs(kind, M_local, N, K, device, seed=1234 + rank)
-    c_full = torch.empty((M, N), dtype=out_dtype(kind), device=device)
-    c_slab = c_full[rank * M_local:(rank + 1) * M_local]
+    from cudaintro_b200.sharded import ShardedGemm
 
-    def step():
-        launch(kind, a, b, c_slab, extra)
-        if world > 1:
-            dist.all_gather_into_tensor(c_full, c_slab)
+    sharded = ShardedGemm(M, N, out_dtype(kind), device)
+    M_local = sharded.part.rows
+    a, b, extra = make_inputs(kind, M_local, N, K, device, seed=1234 + rank)
+    c_slab = sharded.c_slab
+
+    def nccl_step():
+        sharded.step(lambda slab: launch(kind, a, b, slab, extra))
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    fused = None
+    step = nccl_step
+    if world > 1 and args.gather == "fused":
+        from cudaintro_b200.sharded import FusedShardedGemm
+
+        fused = FusedShardedGemm(M, N, out_dtype(kind), device)
+        what = {"bf16": capi.BF16, "f16": capi.F16, "i8": capi.I8, "w8a8": capi.W8A8}[kind]
+
+        def step():
+            fused.step(what, a, b, extra.get("row_scale"), extra.get("col_scale"))
+
+        # untimed check: the fused path must assemble exactly what GEMM + NCCL all-gather assembles
+        nccl_step()
+        step()
+        barrier()
+        if not torch.equal(fused.result().view(torch.uint8), sharded.result().view(torch.uint8)):
+            raise SystemExit(f"rank {rank}: fused GEMM + all-gather differs from GEMM + NCCL all-gather")
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -372,10 +392,20 @@ def main():
         torch.cuda.synchronize()
         gemm_ms = g0.elapsed_time(g1) / args.steps
 
-    t = torch.tensor([ms, gemm_ms], device=device, dtype=torch.float64)
+    gather_ms = 0.0
+    if world > 1:  # the all-gather alone, same buffers
+        barrier()
+        g0.record()
+        for _ in range(args.steps):
+            sharded.gather()
+        g1.record()
+        torch.cuda.synchronize()
+        gather_ms = g0.elapsed_time(g1) / args.steps
+
+    t = torch.tensor([ms, gemm_ms, gather_ms], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, gemm_ms = float(t[0]), float(t[1])
+    ms, gemm_ms, gather_ms = float(t[0]), float(t[1]), float(t[2])
 
     ops_step = 2.0 * M * N * K
     value = ops_step * args.steps / (ms * 1e-3) / 1e12
@@ -415,6 +445,8 @@ def main():
 
     if rank != 0:
         if world > 1:
+            if fused is not None:
+                fused.close()
             dist.barrier()
             dist.destroy_process_group()
         return 0
@@ -441,7 +473,9 @@ def main():
         "scaling": "strong", "vs_baseline": None,
         "dtype": {"bf16": "bf16", "f16": "f16", "i8": "int8", "w8a8": "int8"}[kind], "data": "synthetic",
         "config": {"workload": args.workload, "M": M, "N": N, "K": K, "layout": "row-major",
-                   "parallelism": f"rows of A over {world} GPU(s), B replicated" + (", NCCL all-gather of C" if world > 1 else ""),
+                   "parallelism": f"rows of A over {world} GPU(s), B replicated" + (
+                       "" if world == 1 else (", tiles stored into every rank's C by the GEMM epilogue (peer stores over NVLink)"
+                                              if fused is not None else ", NCCL all-gather of C")),
                    "l2": "inputs larger than L2 (no flush needed)" if (M_local * K + K * N) * in_b > 126e6
                          else "inputs fit L2: back-to-back launches re-use it"},
         "roofline": roofline,
@@ -454,6 +488,12 @@ def main():
     if world > 1:
         line["gemm_phase"] = {"ms": gemm_ms, "value": ops_step / (gemm_ms * 1e-3) / 1e12, "unit": unit,
                               "note": "all ranks' GEMMs without the all-gather"}
+        if fused is not None:
+            line["gemm_plus_nccl_all_gather_ms"] = gemm_ms + gather_ms
+        c_bytes = M * N * out_b
+        line["all_gather"] = {"ms": gather_ms, "bytes_received_per_gpu": c_bytes * (world - 1) // world,
+                              "bus_gbs": c_bytes * (world - 1) / world / (gather_ms * 1e-3) / 1e9,
+                              "note": "NCCL all-gather of C alone; every GPU receives (G-1)/G of C over NVLink"}
 
     if world == 1 and not args.no_suite:
         line["suite"] = side_measurements(device, args.workload)
@@ -462,6 +502,8 @@ def main():
 
     print(json.dumps(line), flush=True)
     if world > 1:
+        if fused is not None:
+            fused.close()
         dist.barrier()
         dist.destroy_process_group()
     return 0

@@ -40,6 +40,14 @@ SIGNATURES = {
     "b200_gemm_naive": (_int, [_int, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
     "b200_gemm_host": (_int, [_int, _p, _p, _p, _i64, _i64, _i64, _int]),
     "b200_host_release": (_int, []),
+    "b200_set_store_policy": (_int, [_int]),
+    "b200_gemm_multi": (_int, [_int, _p, _p, C.POINTER(C.c_void_p), _int, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
+                               _p]),
+    "b200_peer_alloc": (_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "b200_peer_free": (_int, [_p]),
+    "b200_ipc_export": (_int, [_p, _p]),
+    "b200_ipc_import": (_int, [_p, C.POINTER(C.c_void_p)]),
+    "b200_ipc_close": (_int, [_p]),
     "b200_time_gemm": (_int, [_int, _p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _int,
                               C.POINTER(C.c_float), _p]),
 }
@@ -232,3 +240,20 @@ def time_gemm(what, a, b, out, M, N, K, layout=ROW_MAJOR, iters=1, row_scale=Non
 def gemm_host(dtype_code: int, a_np, b_np, c_np, M, N, K, layout=ROW_MAJOR) -> None:
     """Host-buffer entry point: numpy (or any buffer with ctypes data) in, result written to c_np."""
     _check(lib.b200_gemm_host(dtype_code, a_np.ctypes.data, b_np.ctypes.data, c_np.ctypes.data, M, N, K, layout))
+
+
+def set_store_policy(register_stores: bool = False) -> None:
+    """True: C is written straight from registers; False: automatic (staged TMA stores when aligned)."""
+    _check(lib.b200_set_store_policy(1 if register_stores else 0))
+
+
+def gemm_multi(what: int, a, b, dest_ptrs, M: int, N: int, K: int, row_scale=None, col_scale=None) -> None:
+    """Row-major GEMM written to every pointer of `dest_ptrs` (device addresses of the [M, N] slab in
+    each destination buffer, local or peer).  `what` is I8, F16, BF16 or W8A8."""
+    import torch
+
+    arr = (C.c_void_p * len(dest_ptrs))(*[C.c_void_p(int(p)) for p in dest_ptrs])
+    with torch.cuda.device(a.device):
+        _check(lib.b200_gemm_multi(what, a.data_ptr(), b.data_ptr(), arr, len(dest_ptrs),
+                                   0 if row_scale is None else row_scale.data_ptr(),
+                                   0 if col_scale is None else col_scale.data_ptr(), M, N, K, 0, 0, 0, _stream()))

@@ -240,3 +240,55 @@ extern "C" int b200_host_release(void) {
   g_ws.stream = nullptr;
   return B200_OK;
 }
+
+// ------------------------------------------------------------------ several destinations, peer memory
+
+extern "C" int b200_set_store_policy(int register_stores) { return set_store_policy(register_stores); }
+
+extern "C" int b200_gemm_multi(int what, const void* A, const void* B, void* const* C_list, int n_dest,
+                               const float* row_scale, const float* col_scale, int64_t M, int64_t N, int64_t K,
+                               int64_t lda, int64_t ldb, int64_t ldc, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
+  if (lda == 0) lda = K;
+  if (ldb == 0) ldb = N;
+  if (ldc == 0) ldc = N;
+  int kind, epi;
+  switch (what) {
+    case B200_I8: kind = KIND_I8; epi = EPI_I32; break;
+    case B200_F16: kind = KIND_F16; epi = EPI_F16; break;
+    case B200_BF16: kind = KIND_BF16; epi = EPI_BF16; break;
+    case B200_W8A8: kind = KIND_I8; epi = EPI_W8A8_BF16; break;
+    default: return fail(B200_ERR_BAD_ARGUMENT, "b200_gemm_multi: unsupported type %d", what);
+  }
+  return launch_umma_gemm_multi(kind, epi, A, B, C_list, n_dest, M, N, K, lda, ldb, ldc, false, row_scale,
+                                col_scale, 0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_peer_alloc(size_t bytes, void** ptr) {
+  if (!ptr || bytes == 0) return fail(B200_ERR_BAD_ARGUMENT, "peer_alloc: bad argument");
+  B200_CUDA_TRY(cudaMalloc(ptr, bytes));
+  return B200_OK;
+}
+extern "C" int b200_peer_free(void* ptr) {
+  if (ptr) B200_CUDA_TRY(cudaFree(ptr));
+  return B200_OK;
+}
+extern "C" int b200_ipc_export(void* ptr, void* handle64) {
+  if (!ptr || !handle64) return fail(B200_ERR_BAD_ARGUMENT, "ipc_export: null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  B200_CUDA_TRY(cudaIpcGetMemHandle(&h, ptr));
+  memcpy(handle64, &h, sizeof(h));
+  return B200_OK;
+}
+extern "C" int b200_ipc_import(const void* handle64, void** ptr) {
+  if (!ptr || !handle64) return fail(B200_ERR_BAD_ARGUMENT, "ipc_import: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  B200_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return B200_OK;
+}
+extern "C" int b200_ipc_close(void* ptr) {
+  if (ptr) B200_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return B200_OK;
+}

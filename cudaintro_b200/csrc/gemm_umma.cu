@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstring>
 #include <mutex>
 
 #include "internal.h"
@@ -57,19 +58,29 @@ struct Tile {
   static constexpr int B_BYTES = BN_CTA * 128;
   static constexpr int SPAN_BYTES = BK * 128;  // one span of B: BK k-rows of 128 bytes
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES_FIT = (kSmemBudget - 2048) / STAGE_BYTES;
+  static constexpr int STAGING_BYTES = 2 * BM * 128;  // two 128-row x 128-byte output tiles for the TMA stores
+  static constexpr int STAGES_FIT = (kSmemBudget - 2048 - STAGING_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // BN is a power of two here
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+constexpr int kMaxDest = 8;  // copies of C one launch can write (this GPU's and up to 7 peers')
+
+enum StoreMode { STORE_SCALAR = 0, STORE_VECTOR = 1, STORE_TMA = 2 };
+
+struct CMaps {
+  CUtensorMap m[kMaxDest];
 };
 
 struct GemmArgs {
-  void* C;
+  void* C[kMaxDest];  // same slab of C in every destination buffer
+  int n_dest;
   int64_t ldc;
   int M, N, K;
   int tiles_m, tiles_n;
   int group_m;  // m-tiles per group of the tile order
-  int c_vec;  // 1 when C and ldc allow 16-byte stores
+  int store_mode;  // StoreMode: how the epilogue writes C
   const float* row_scale;
   const float* col_scale;
 };
@@ -89,26 +100,15 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   nb = r / gm;
 }
 
+// Converts 32 accumulator columns of one row into output words: 32 words for 4-byte outputs,
+// 16 words (two elements each) for 2-byte outputs.
 template <int EPI>
-__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, const uint32_t (&v)[32],
-                                            float rs) {
-  // One thread owns row `row`, columns [n0, n0 + 32).
-  constexpr int OUT_BYTES = (EPI == EPI_I32 || EPI == EPI_F32) ? 4 : 2;
-  char* crow = static_cast<char*>(p.C) + (int64_t(row) * p.ldc + n0) * OUT_BYTES;
-  bool full = p.c_vec && n0 + 32 <= p.N;
+__device__ __forceinline__ void pack_chunk(const GemmArgs& p, int n0, const uint32_t (&v)[32], float rs,
+                                           uint32_t (&w)[32]) {
   if constexpr (EPI == EPI_I32 || EPI == EPI_F32) {
-    if (full) {
-      uint4* dst = reinterpret_cast<uint4*>(crow);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-    } else {
-      uint32_t* dst = reinterpret_cast<uint32_t*>(crow);
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (n0 + i < p.N) dst[i] = v[i];
-    }
+    for (int i = 0; i < 32; ++i) w[i] = v[i];
   } else {
-    uint32_t packed[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       float x0, x1;
@@ -124,22 +124,38 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, 
       }
       if constexpr (EPI == EPI_F16) {
         __half2 h = __floats2half2_rn(x0, x1);
-        packed[i] = *reinterpret_cast<uint32_t*>(&h);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
       } else {
         __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-        packed[i] = *reinterpret_cast<uint32_t*>(&h);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
       }
     }
+  }
+}
+
+// Register path of the epilogue: one thread owns row `row`, columns [n0, n0 + 32), and writes
+// them to every destination with 16-byte stores (or element by element when C is not aligned).
+template <int EPI>
+__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, const uint32_t (&w)[32]) {
+  constexpr int OUT_BYTES = (EPI == EPI_I32 || EPI == EPI_F32) ? 4 : 2;
+  constexpr int WORDS = 32 * OUT_BYTES / 4;
+  const bool full = p.store_mode != STORE_SCALAR && n0 + 32 <= p.N;
+  for (int g = 0; g < p.n_dest; ++g) {
+    char* crow = static_cast<char*>(p.C[g]) + (int64_t(row) * p.ldc + n0) * OUT_BYTES;
     if (full) {
       uint4* dst = reinterpret_cast<uint4*>(crow);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      for (int i = 0; i < WORDS / 4; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    } else if constexpr (OUT_BYTES == 4) {
+      uint32_t* dst = reinterpret_cast<uint32_t*>(crow);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (n0 + i < p.N) dst[i] = w[i];
     } else {
       uint16_t* dst = reinterpret_cast<uint16_t*>(crow);
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (n0 + i < p.N) dst[i] = uint16_t(packed[i >> 1] >> ((i & 1) * 16));
+        if (n0 + i < p.N) dst[i] = uint16_t(w[i >> 1] >> ((i & 1) * 16));
     }
   }
 }
@@ -147,19 +163,21 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, 
 template <int KIND, int BN, bool B_NK, int EPI, int CG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmArgs p) {
+                 const __grid_constant__ CMaps tmap_c, const GemmArgs p) {
   using T = Tile<KIND, BN, CG>;
   constexpr int TILE_M = BM * CG;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes: align the stage ring to that.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T::STAGES * T::STAGE_BYTES);
+  uint8_t* staging = smem + T::STAGES * T::STAGE_BYTES;  // two output tiles, 128 rows x 128 bytes each
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + T::STAGING_BYTES);
   uint64_t* full_bar = bars;                   // [STAGES] producer(s) -> MMA   (pair: the leader's is used)
   uint64_t* empty_bar = bars + T::STAGES;      // [STAGES] MMA -> producer      (pair: one in each CTA)
   uint64_t* acc_full = bars + 2 * T::STAGES;   // [2] MMA -> epilogue           (pair: one in each CTA)
   uint64_t* acc_empty = acc_full + 2;          // [2] epilogue -> MMA           (pair: the leader's is used)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* epi_go = tmem_slot + 2;  // epilogue warps: "this tile's accumulator arrived"
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -308,27 +326,78 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
+    constexpr int OUT_BYTES = (EPI == EPI_I32 || EPI == EPI_F32) ? 4 : 2;
+    constexpr int BOX_COLS = 128 / OUT_BYTES;     // columns of C in one 128-byte row of an output tile
+    constexpr int CHUNKS_PER_BOX = BOX_COLS / 32;  // 32-column TMEM loads per output tile
+    constexpr int UNITS = 8 / CHUNKS_PER_BOX;      // 16-byte units one load contributes to its row
+    constexpr int kEpiThreads = 128;
     const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter + 32)
+    const int r_in_tile = quarter * 32 + lane;
+    const bool store_thread = warp == 2 && lane == 0;
+    uint32_t boxes = 0;
     int it = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mb, nb;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
       const int ab = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      if (!mbar_wait_bounded(&acc_full[ab], acc_phase, abort_flag)) break;
+      // One warp polls the barrier; all four then agree on the outcome, so that they always meet at
+      // the same hardware barriers below even when the wait had to be given up.
+      if (warp == 2) {
+        const bool ok = mbar_wait_bounded(&acc_full[ab], acc_phase, abort_flag);
+        if (lane == 0) *epi_go = ok ? 1u : 0u;
+      }
+      named_barrier_sync(2, kEpiThreads);
+      if (*epi_go == 0u) break;
       tc_fence_after_sync();
-      const int row = mb * TILE_M + int(cta_rank) * BM + quarter * 32 + lane;
+      const int tile_row0 = mb * TILE_M + int(cta_rank) * BM;
+      const int row = tile_row0 + r_in_tile;
       float rs = 0.f;
       if constexpr (EPI == EPI_W8A8_BF16) rs = row < p.M ? __ldg(p.row_scale + row) : 0.f;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(ab * BN);
+      if (p.store_mode == STORE_TMA) {
+        // Stage 128 x 128-byte output tiles in shared memory (swizzled like the tensor map expects)
+        // and let TMA write them: whole rows per request, clipped at the edges of C, one request
+        // per destination buffer.
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int n0 = nb * BN + c * 32;
-        if (n0 >= p.N) break;  // uniform across the warp
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + uint32_t(c * 32), v);
-        tmem_ld_wait();
-        if (row < p.M) store_chunk<EPI>(p, row, n0, v, rs);
+        for (int bx = 0; bx < BN / BOX_COLS; ++bx) {
+          const int n0 = nb * BN + bx * BOX_COLS;
+          if (n0 >= p.N) break;  // uniform across the four warps
+          uint8_t* buf = staging + (boxes & 1u) * (BM * 128);
+          if (store_thread) tma_store_wait_read<1>();  // the store that last used `buf` has read it
+          named_barrier_sync(1, kEpiThreads);
+#pragma unroll
+          for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
+            uint32_t v[32], w[32];
+            tmem_ld_32x32(taddr + uint32_t(bx * BOX_COLS + h * 32), v);
+            tmem_ld_wait();
+            pack_chunk<EPI>(p, n0 + h * 32, v, rs, w);
+#pragma unroll
+            for (int i = 0; i < UNITS; ++i) {
+              const int unit = h * UNITS + i;
+              *reinterpret_cast<uint4*>(buf + r_in_tile * 128 + ((unit ^ (r_in_tile & 7)) << 4)) =
+                  make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            }
+          }
+          fence_proxy_async_smem();
+          named_barrier_sync(1, kEpiThreads);
+          if (store_thread) {
+            for (int g = 0; g < p.n_dest; ++g) tma_store_2d(&tmap_c.m[g], buf, n0, tile_row0);
+            tma_store_commit();
+          }
+          ++boxes;
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int n0 = nb * BN + c * 32;
+          if (n0 >= p.N) break;  // uniform across the warp
+          uint32_t v[32], w[32];
+          tmem_ld_32x32(taddr + uint32_t(c * 32), v);
+          tmem_ld_wait();
+          pack_chunk<EPI>(p, n0, v, rs, w);
+          if (row < p.M) store_chunk<EPI>(p, row, n0, w);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -337,6 +406,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         else mbar_arrive(&acc_empty[ab]);
       }
     }
+    if (store_thread) tma_store_wait_all<0>();  // every output tile has left for global memory
   }
 
   // Every role gets here: either its loop ended or its wait was abandoned.
@@ -399,6 +469,25 @@ int make_map(CUtensorMap* map, int kind, const void* base, int64_t rows, int64_t
   return B200_OK;
 }
 
+// Tensor map for storing 128-row x 128-byte tiles of a row-major [rows, cols] C.
+int make_c_map(CUtensorMap* map, int epi, void* base, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const int elem = (epi == EPI_I32 || epi == EPI_F32) ? 4 : 2;
+  CUtensorMapDataType dt = epi == EPI_I32   ? CU_TENSOR_MAP_DATA_TYPE_INT32
+                           : epi == EPI_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : epi == EPI_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                            : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(ld) * cuuint64_t(elem)};
+  cuuint32_t box[2] = {cuuint32_t(128 / elem), cuuint32_t(BM)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled (C) failed with CUresult %d", int(r));
+  return B200_OK;
+}
+
 int sm_count_of_current_device(int* out) {
   static int cached[64] = {0};
   int dev = 0;
@@ -437,6 +526,14 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
     rc = make_map(&mb, KIND, B, planes * args.K, args.N, ldb, T::SPAN < T::BN_CTA ? T::SPAN : T::BN_CTA, T::BK,
                   /*chunks32=*/KIND == KIND_TF32);
   if (rc) return rc;
+  CMaps mc;
+  memset(&mc, 0, sizeof(mc));
+  if (args.store_mode == STORE_TMA) {
+    for (int g = 0; g < args.n_dest; ++g) {
+      rc = make_c_map(&mc.m[g], EPI, args.C[g], args.M, args.N, args.ldc);
+      if (rc) return rc;
+    }
+  }
   int sms = 0;
   rc = sm_count_of_current_device(&sms);
   if (rc) return rc;
@@ -455,10 +552,10 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ma, mb, args));
+    B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mc, args));
   } else {
     int grid = tiles < sms ? tiles : sms;
-    kernel<<<grid, kThreads, T::SMEM_BYTES, stream>>>(ma, mb, args);
+    kernel<<<grid, kThreads, T::SMEM_BYTES, stream>>>(ma, mb, mc, args);
     B200_CUDA_TRY(cudaGetLastError());
   }
   return B200_OK;
@@ -479,6 +576,7 @@ int launch_major(bool b_nk, const void* A, const void* B, const GemmArgs& args, 
 }
 
 int g_force_cg = 0, g_force_bn = 0, g_group_rows = 0;  // 0 = automatic; set through b200_set_tile_policy
+int g_force_store = 0;                                  // 0 = automatic, STORE_VECTOR = register stores
 
 template <int KIND, int EPI>
 int launch_bn(int bn, int cg, bool b_nk, const void* A, const void* B, GemmArgs args, int64_t lda, int64_t ldb,
@@ -513,6 +611,11 @@ int set_tile_policy(int cg, int bn, int group_rows) {
   return B200_OK;
 }
 
+int set_store_policy(int register_stores) {
+  g_force_store = register_stores ? STORE_VECTOR : 0;
+  return B200_OK;
+}
+
 int read_and_clear_umma_status(cudaStream_t stream, uint32_t* out) {
   uint32_t zero = 0;
   B200_CUDA_TRY(cudaStreamSynchronize(stream));
@@ -525,7 +628,19 @@ int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, i
                      int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
                      const float* row_scale, const float* col_scale, int force_bn,
                      cudaStream_t stream) {
-  if (!A || !B || !C) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
+  void* one[1] = {C};
+  return launch_umma_gemm_multi(kind, epi, A, B, one, 1, M, N, K, lda, ldb, ldc, b_is_nk, row_scale, col_scale,
+                                force_bn, stream);
+}
+
+int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void* const* C_list, int n_dest,
+                           int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
+                           const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream) {
+  if (!A || !B || !C_list) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
+  if (n_dest < 1 || n_dest > kMaxDest)
+    return fail(B200_ERR_BAD_ARGUMENT, "number of destinations must be between 1 and %d", kMaxDest);
+  for (int g = 0; g < n_dest; ++g)
+    if (!C_list[g]) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer (destination %d)", g);
   if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
   if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30))
     return fail(B200_ERR_TOO_LARGE, "a dimension exceeds 2^30");
@@ -541,20 +656,27 @@ int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, i
                 "tensor-core GEMM needs 16-byte aligned A and B pointers and leading dimensions "
                 "(lda=%lld ldb=%lld, element %d bytes)",
                 (long long)lda, (long long)ldb, elem);
-  if (reinterpret_cast<uintptr_t>(C) % out_elem)
-    return fail(B200_ERR_UNSUPPORTED, "C is not aligned to its element size");
+  bool c_aligned16 = (ldc * out_elem) % 16 == 0;
+  for (int g = 0; g < n_dest; ++g) {
+    if (reinterpret_cast<uintptr_t>(C_list[g]) % out_elem)
+      return fail(B200_ERR_UNSUPPORTED, "C is not aligned to its element size");
+    if (reinterpret_cast<uintptr_t>(C_list[g]) % 16) c_aligned16 = false;
+  }
   if (epi == EPI_W8A8_BF16 && (!row_scale || !col_scale))
     return fail(B200_ERR_BAD_ARGUMENT, "null scale pointer");
 
   GemmArgs args;
-  args.C = C;
+  memset(&args, 0, sizeof(args));
+  for (int g = 0; g < n_dest; ++g) args.C[g] = C_list[g];
+  args.n_dest = n_dest;
   args.ldc = ldc;
   args.M = int(M);
   args.N = int(N);
   args.K = int(K);
   args.tiles_m = int((M + BM - 1) / BM);
   args.tiles_n = 0;
-  args.c_vec = ((ldc * out_elem) % 16 == 0 && reinterpret_cast<uintptr_t>(C) % 16 == 0) ? 1 : 0;
+  // Aligned C: staged TMA stores (or 16-byte register stores when forced); otherwise element by element.
+  args.store_mode = !c_aligned16 ? STORE_SCALAR : (g_force_store == STORE_VECTOR ? STORE_VECTOR : STORE_TMA);
   args.row_scale = row_scale;
   args.col_scale = col_scale;
 

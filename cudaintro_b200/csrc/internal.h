@@ -28,6 +28,14 @@ int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, i
                      const float* row_scale, const float* col_scale, int force_bn,
                      cudaStream_t stream);
 
+// Same product written to n_dest destination buffers at once (this GPU's C and peers' copies).
+int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void* const* C_list, int n_dest,
+                           int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
+                           const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream);
+
+// 1 = write C from registers with 16-byte stores instead of staged TMA stores; 0 = automatic.
+int set_store_policy(int register_stores);
+
 // Overrides the automatic choice of CTA grouping (1 or 2 CTAs per tile) and tile width; 0 = automatic.
 int set_tile_policy(int cg, int bn, int group_rows);
 

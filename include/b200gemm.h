@@ -23,6 +23,7 @@
 #ifndef B200GEMM_H_
 #define B200GEMM_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -118,6 +119,32 @@ int b200_gemm_f32_3xtf32_static(const float* A, const float* B, float* C, int64_
 int b200_gemm_w8a8_bf16(const int8_t* A, const int8_t* B, const float* row_scale,
                         const float* col_scale, void* C, int64_t M, int64_t N, int64_t K,
                         int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
+/* Row-major GEMM whose result is written to n_dest (1..8) buffers at once: C_list[g] points at
+ * the same [M, N] slab (leading dimension ldc) inside destination g.  Destinations may be this
+ * GPU's memory or peer GPUs' memory mapped into this process (b200_ipc_import): the epilogue
+ * then sends every finished tile over NVLink while later tiles are still being computed, which
+ * is how a row-sharded product places its rows in every rank's copy of C without a separate
+ * all-gather.  `what` is B200_I8, B200_F16, B200_BF16 or B200_W8A8 (the scales are read only
+ * for B200_W8A8).  Remote copies are complete when the kernel has finished on the writing GPU;
+ * readers on other GPUs must order themselves after that (any cross-rank barrier).  No
+ * counterpart in the reference (it runs on one GPU). */
+int b200_gemm_multi(int what, const void* A, const void* B, void* const* C_list, int n_dest,
+                    const float* row_scale, const float* col_scale, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
+/* Device memory that other processes on the same machine can map: allocate, export a 64-byte
+ * handle, import a peer's handle (enables peer access on first use), close, free. */
+int b200_peer_alloc(size_t bytes, void** ptr);
+int b200_peer_free(void* ptr);
+int b200_ipc_export(void* ptr, void* handle64);
+int b200_ipc_import(const void* handle64, void** ptr);
+int b200_ipc_close(void* ptr);
+
+/* 1 = the tensor-core kernels write C straight from registers (16-byte stores) instead of
+ * staging tiles in shared memory for TMA stores; 0 = automatic (TMA stores whenever C and ldc
+ * are 16-byte aligned).  For tests and measurements; results do not depend on it. */
+int b200_set_store_policy(int register_stores);
 
 /* Symmetric absmax quantiser of a row-major fp32 [R, C] matrix to int8 (same shape):
  *   along = 0: scale[r] = max_c |x[r][c]| / 127  (R scales);  along = 1: per column (C scales);
