@@ -47,7 +47,11 @@ METRIC = "int8 TOPS & bf16/fp16 TFLOPS per GPU at 8192^3; % of dense tensor peak
 
 # DRAM bytes per launch of the dominant kernel measured by ncu (dram__bytes_read.sum +
 # dram__bytes_write.sum); None until a capture of that workload is summarised under profiles/.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    "bf16_8192": 926264320 + 126121984,   # profiles/gemm_umma_bf16_8192x8192x8192.md
+    "int8_8192": 303960576 + 241032192,   # profiles/gemm_umma_int8_8192x8192x8192.md
+    "w8a8": 841799424 + 458604544,        # profiles/gemm_umma_w8a8_8192x28672x8192.md
+}
 
 
 def measured_peaks():
@@ -303,6 +307,8 @@ def main():
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N>1: fused = the GEMM epilogue stores each tile into every rank's C over NVLink; "
                          "nccl = GEMM, then NCCL all-gather")
+    ap.add_argument("--register-stores", action="store_true",
+                    help="write C straight from registers instead of staged TMA stores (for comparison)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -330,6 +336,8 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     kind, M, N, K, in_b, out_b, unit = WORKLOADS[args.workload]
+    if args.register_stores:
+        capi.set_store_policy(True)
     from cudaintro_b200.sharded import ShardedGemm
 
     sharded = ShardedGemm(M, N, out_dtype(kind), device)
@@ -402,10 +410,21 @@ def main():
         torch.cuda.synchronize()
         gather_ms = g0.elapsed_time(g1) / args.steps
 
-    t = torch.tensor([ms, gemm_ms, gather_ms], device=device, dtype=torch.float64)
+    fused_kernel_ms = 0.0
+    if fused is not None:  # the fused kernel without the completion marker that ends a step
+        barrier()
+        g0.record()
+        for _ in range(args.steps):
+            capi.gemm_multi(what, a, b, fused.slab_ptrs, fused.part.rows, N, K, extra.get("row_scale"),
+                            extra.get("col_scale"))
+        g1.record()
+        torch.cuda.synchronize()
+        fused_kernel_ms = g0.elapsed_time(g1) / args.steps
+
+    t = torch.tensor([ms, gemm_ms, gather_ms, fused_kernel_ms], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, gemm_ms, gather_ms = float(t[0]), float(t[1]), float(t[2])
+    ms, gemm_ms, gather_ms, fused_kernel_ms = float(t[0]), float(t[1]), float(t[2]), float(t[3])
 
     ops_step = 2.0 * M * N * K
     value = ops_step * args.steps / (ms * 1e-3) / 1e12
@@ -490,6 +509,7 @@ def main():
                               "note": "all ranks' GEMMs without the all-gather"}
         if fused is not None:
             line["gemm_plus_nccl_all_gather_ms"] = gemm_ms + gather_ms
+            line["fused_kernel_ms"] = fused_kernel_ms
         c_bytes = M * N * out_b
         line["all_gather"] = {"ms": gather_ms, "bytes_received_per_gpu": c_bytes * (world - 1) // world,
                               "bus_gbs": c_bytes * (world - 1) / world / (gather_ms * 1e-3) / 1e9,

@@ -41,6 +41,7 @@ SIGNATURES = {
     "b200_gemm_host": (_int, [_int, _p, _p, _p, _i64, _i64, _i64, _int]),
     "b200_host_release": (_int, []),
     "b200_set_store_policy": (_int, [_int]),
+    "b200_set_split_k": (_int, [_int]),
     "b200_gemm_multi": (_int, [_int, _p, _p, C.POINTER(C.c_void_p), _int, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                _p]),
     "b200_peer_alloc": (_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
@@ -245,6 +246,11 @@ def gemm_host(dtype_code: int, a_np, b_np, c_np, M, N, K, layout=ROW_MAJOR) -> N
 def set_store_policy(register_stores: bool = False) -> None:
     """True: C is written straight from registers; False: automatic (staged TMA stores when aligned)."""
     _check(lib.b200_set_store_policy(1 if register_stores else 0))
+
+
+def set_split_k(splits: int = 0) -> None:
+    """0 or 1: K is not split (default); n: cut K into n ranges (single-CTA tensor-core kernels)."""
+    _check(lib.b200_set_split_k(splits))
 
 
 def gemm_multi(what: int, a, b, dest_ptrs, M: int, N: int, K: int, row_scale=None, col_scale=None) -> None:

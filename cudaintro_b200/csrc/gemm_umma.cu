@@ -81,6 +81,13 @@ struct GemmArgs {
   int tiles_m, tiles_n;
   int group_m;  // m-tiles per group of the tile order
   int store_mode;  // StoreMode: how the epilogue writes C
+  // Split-K (single CTAs only): K is cut into `splits` ranges of `kb_per_split` k-blocks, one work
+  // item each; partial accumulators go to `ws` ([tile][split][128][BN] 32-bit words) and the item that
+  // finishes a tile last (per `counters[tile]`, zero on entry, reset on exit) adds them up and stores C.
+  int splits;
+  int kb_per_split;
+  uint32_t* ws;
+  uint32_t* counters;
   const float* row_scale;
   const float* col_scale;
 };
@@ -100,17 +107,17 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   nb = r / gm;
 }
 
-// Converts 32 accumulator columns of one row into output words: 32 words for 4-byte outputs,
-// 16 words (two elements each) for 2-byte outputs.
-template <int EPI>
-__device__ __forceinline__ void pack_chunk(const GemmArgs& p, int n0, const uint32_t (&v)[32], float rs,
-                                           uint32_t (&w)[32]) {
+// Converts W accumulator columns of one row into output words: W words for 4-byte outputs,
+// W/2 words (two elements each) for 2-byte outputs.
+template <int EPI, int W = 32>
+__device__ __forceinline__ void pack_chunk(const GemmArgs& p, int n0, const uint32_t (&v)[W], float rs,
+                                           uint32_t (&w)[W]) {
   if constexpr (EPI == EPI_I32 || EPI == EPI_F32) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) w[i] = v[i];
+    for (int i = 0; i < W; ++i) w[i] = v[i];
   } else {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < W / 2; ++i) {
       float x0, x1;
       if constexpr (EPI == EPI_W8A8_BF16) {
         // (float(acc) * row_scale) * col_scale, each step rounded once, then to bf16
@@ -133,13 +140,13 @@ __device__ __forceinline__ void pack_chunk(const GemmArgs& p, int n0, const uint
   }
 }
 
-// Register path of the epilogue: one thread owns row `row`, columns [n0, n0 + 32), and writes
+// Register path of the epilogue: one thread owns row `row`, columns [n0, n0 + W), and writes
 // them to every destination with 16-byte stores (or element by element when C is not aligned).
-template <int EPI>
-__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, const uint32_t (&w)[32]) {
+template <int EPI, int W = 32>
+__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, const uint32_t (&w)[W]) {
   constexpr int OUT_BYTES = (EPI == EPI_I32 || EPI == EPI_F32) ? 4 : 2;
-  constexpr int WORDS = 32 * OUT_BYTES / 4;
-  const bool full = p.store_mode != STORE_SCALAR && n0 + 32 <= p.N;
+  constexpr int WORDS = W * OUT_BYTES / 4;
+  const bool full = p.store_mode != STORE_SCALAR && n0 + W <= p.N;
   for (int g = 0; g < p.n_dest; ++g) {
     char* crow = static_cast<char*>(p.C[g]) + (int64_t(row) * p.ldc + n0) * OUT_BYTES;
     if (full) {
@@ -149,12 +156,12 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, 
     } else if constexpr (OUT_BYTES == 4) {
       uint32_t* dst = reinterpret_cast<uint32_t*>(crow);
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
+      for (int i = 0; i < W; ++i)
         if (n0 + i < p.N) dst[i] = w[i];
     } else {
       uint16_t* dst = reinterpret_cast<uint16_t*>(crow);
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
+      for (int i = 0; i < W; ++i)
         if (n0 + i < p.N) dst[i] = uint16_t(w[i >> 1] >> ((i & 1) * 16));
     }
   }
@@ -184,7 +191,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t cta_rank = CG == 2 ? cluster_cta_rank() : 0u;  // 0 = leader of the pair
   const int first_tile = CG == 2 ? int(blockIdx.x >> 1) : int(blockIdx.x);
   const int tile_step = CG == 2 ? int(gridDim.x >> 1) : int(gridDim.x);
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.tiles_m * p.tiles_n * p.splits;  // work items: (tile, K range)
   const int num_kb = (p.K + T::BK - 1) / T::BK;
   // Split-operand fp32 (3xTF32): A and B each arrive as two stacked planes, low parts on top of
   // high parts, and K is walked three times: lo*hi, then hi*lo, then hi*hi (small terms first).
@@ -228,16 +235,20 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int it = 0;
       for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
         int mb, nb;
-        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+        const int tile = t / p.splits, split = t - tile * p.splits;
+        tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+        const int kb_first = split * p.kb_per_split;
+        const int kb_count = p.splits == 1 ? total_kb : min(p.kb_per_split, num_kb - kb_first);
         // Every other tile walks K backwards: a tile then starts on the k-blocks its predecessor
         // touched last, which are the ones still in L2 (a forward-only sweep over a slab larger
         // than the cache would evict each block just before it is needed again).
         const bool k_reversed = (it & 1) != 0;
         const int m0 = mb * TILE_M + int(cta_rank) * BM;
         const int n0 = nb * BN + int(cta_rank) * T::BN_CTA;
-        for (int kbt = 0; kbt < total_kb; ++kbt) {
+        for (int kbt = 0; kbt < kb_count; ++kbt) {
           const int pass = X3 ? kbt / num_kb : 0;
-          const int kb = k_reversed ? num_kb - 1 - (kbt - pass * num_kb) : kbt - pass * num_kb;
+          const int kb = p.splits > 1 ? kb_first + kbt
+                                      : (k_reversed ? num_kb - 1 - (kbt - pass * num_kb) : kbt - pass * num_kb);
           const int a_row0 = (X3 && pass != 0) ? p.M : 0;                       // plane 1 = high parts
           const int b_row0 = (X3 && pass != 1) ? (B_NK ? p.N : p.K) : 0;
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -293,7 +304,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!mbar_wait_bounded(&acc_empty[ab], acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);
-        for (int kb = 0; kb < total_kb; ++kb) {
+        const int kb_count =
+            p.splits == 1 ? total_kb : min(p.kb_per_split, num_kb - (t % p.splits) * p.kb_per_split);
+        for (int kb = 0; kb < kb_count; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * T::STAGE_BYTES);
@@ -338,7 +351,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int it = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mb, nb;
-      tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+      const int tile = t / p.splits, split = t - tile * p.splits;
+      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
       const int ab = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       // One warp polls the barrier; all four then agree on the outcome, so that they always meet at
@@ -382,10 +396,33 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           fence_proxy_async_smem();
           named_barrier_sync(1, kEpiThreads);
           if (store_thread) {
-            for (int g = 0; g < p.n_dest; ++g) tma_store_2d(&tmap_c.m[g], buf, n0, tile_row0);
+            // Start each tile at a different destination (rotating with the CTA and the tile count):
+            // when the destinations are peer GPUs, every sender then spreads its traffic over all
+            // receivers at all times instead of all senders hitting the same receiver together.
+            int g = int((uint32_t(first_tile) + boxes) % uint32_t(p.n_dest));
+            for (int i = 0; i < p.n_dest; ++i) {
+              tma_store_2d(&tmap_c.m[g], buf, n0, tile_row0);
+              if (++g == p.n_dest) g = 0;
+            }
             tma_store_commit();
           }
           ++boxes;
+        }
+      } else if (p.splits > 1) {
+        // Split-K: park this K range's raw accumulator in the workspace; whoever completes the tile
+        // adds the ranges up in range order (so the result does not depend on who came last).
+        uint32_t* part = p.ws + ((size_t(tile) * p.splits + split) * BM + r_in_tile) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (nb * BN + c * 32 >= p.N) break;
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + uint32_t(c * 32), v);
+          tmem_ld_wait();
+          if (row < p.M) {
+            uint4* dst = reinterpret_cast<uint4*>(part + c * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          }
         }
       } else {
 #pragma unroll 1
@@ -404,6 +441,48 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (lane == 0) {
         if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[ab]), 0));
         else mbar_arrive(&acc_empty[ab]);
+      }
+      if (p.splits > 1) {
+        __threadfence();  // this thread's partial row is visible device-wide before the count goes up
+        named_barrier_sync(1, kEpiThreads);
+        if (store_thread) {
+          const uint32_t done = atomicAdd(p.counters + tile, 1u);
+          const bool last = done == uint32_t(p.splits - 1);
+          if (last) p.counters[tile] = 0;  // ready for the next launch
+          *epi_go = last ? 1u : 0u;
+        }
+        named_barrier_sync(1, kEpiThreads);
+        if (*epi_go != 0u) {
+          // All 128 threads share the tile: a unit is 8 consecutive columns of one row, consecutive
+          // threads take consecutive units, so reads of the partial sums and stores to C are coalesced
+          // and every thread has all its loads in flight at once.
+          __threadfence();
+          const int valid_rows = min(BM, p.M - tile_row0);
+          const uint32_t* base = p.ws + size_t(tile) * p.splits * BM * BN;
+          for (int u = r_in_tile; u < valid_rows * (BN / 8); u += kEpiThreads) {
+            const int ur = u / (BN / 8), uc = (u - ur * (BN / 8)) * 8;
+            const int n0 = nb * BN + uc;
+            if (n0 >= p.N) continue;
+            uint32_t v[8], w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0u;
+            for (int sp = 0; sp < p.splits; ++sp) {
+              const uint4* src = reinterpret_cast<const uint4*>(base + (size_t(sp) * BM + ur) * BN + uc);
+              const uint4 u0 = __ldcg(src), u1 = __ldcg(src + 1);
+              const uint32_t in[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                if constexpr (KIND == KIND_I8) v[i] += in[i];
+                else v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(in[i]));
+              }
+            }
+            float urs = 0.f;
+            if constexpr (EPI == EPI_W8A8_BF16) urs = __ldg(p.row_scale + tile_row0 + ur);
+            pack_chunk<EPI, 8>(p, n0, v, urs, w);
+            store_chunk<EPI, 8>(p, tile_row0 + ur, n0, w);
+          }
+        }
+        named_barrier_sync(1, kEpiThreads);  // epi_go is rewritten by the next item
       }
     }
     if (store_thread) tma_store_wait_all<0>();  // every output tile has left for global memory
@@ -537,7 +616,7 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
   int sms = 0;
   rc = sm_count_of_current_device(&sms);
   if (rc) return rc;
-  int tiles = args.tiles_m * args.tiles_n;
+  int tiles = args.tiles_m * args.tiles_n * args.splits;  // work items
   if constexpr (CG == 2) {
     int pairs = tiles < sms / 2 ? tiles : sms / 2;
     cudaLaunchConfig_t cfg = {};
@@ -577,6 +656,34 @@ int launch_major(bool b_nk, const void* A, const void* B, const GemmArgs& args, 
 
 int g_force_cg = 0, g_force_bn = 0, g_group_rows = 0;  // 0 = automatic; set through b200_set_tile_policy
 int g_force_store = 0;                                  // 0 = automatic, STORE_VECTOR = register stores
+int g_force_splits = 0;                                 // 0 = automatic, 1 = never split K, n = n ranges
+
+// Stream-ordered memory pool of the split-K workspaces, one per device.  It keeps what it has
+// handed out before (release threshold at the maximum), so that after the first call an
+// allocation is a host-side bookkeeping step and never reaches the driver's allocator.
+int split_k_pool(cudaMemPool_t* out) {
+  static std::mutex mu;
+  static cudaMemPool_t pools[64] = {nullptr};
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200_ERR_UNSUPPORTED, "device ordinal %d is beyond the pool table", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!pools[dev]) {
+    cudaMemPoolProps props;
+    memset(&props, 0, sizeof(props));
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    cudaMemPool_t pool = nullptr;
+    B200_CUDA_TRY(cudaMemPoolCreate(&pool, &props));
+    uint64_t keep = ~uint64_t(0);
+    B200_CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+    pools[dev] = pool;
+  }
+  *out = pools[dev];
+  return B200_OK;
+}
 
 template <int KIND, int EPI>
 int launch_bn(int bn, int cg, bool b_nk, const void* A, const void* B, GemmArgs args, int64_t lda, int64_t ldb,
@@ -611,6 +718,12 @@ int set_tile_policy(int cg, int bn, int group_rows) {
   return B200_OK;
 }
 
+int set_split_k(int splits) {
+  if (splits < 0 || splits > 64) return fail(B200_ERR_BAD_ARGUMENT, "split-K: between 0 (automatic) and 64 ranges");
+  g_force_splits = splits;
+  return B200_OK;
+}
+
 int set_store_policy(int register_stores) {
   g_force_store = register_stores ? STORE_VECTOR : 0;
   return B200_OK;
@@ -622,6 +735,11 @@ int read_and_clear_umma_status(cudaStream_t stream, uint32_t* out) {
   B200_CUDA_TRY(cudaMemcpyFromSymbol(out, g_umma_status, sizeof(uint32_t)));
   if (*out) B200_CUDA_TRY(cudaMemcpyToSymbol(g_umma_status, &zero, sizeof(uint32_t)));
   return B200_OK;
+}
+
+namespace {
+int launch_kind(int kind, int epi, int bn, int cg, bool b_is_nk, const void* A, const void* B, const GemmArgs& args,
+                int64_t lda, int64_t ldb, cudaStream_t stream);
 }
 
 int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, int64_t M, int64_t N,
@@ -692,12 +810,67 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   }
   if (cg == 2) bn = 256;
   if (bn == 0) {
-    // Widest tile that still gives every SM something to do.
-    bn = 256;
-    while (bn > 64 && int64_t(args.tiles_m) * ((N + bn - 1) / bn) < sms) bn >>= 1;
+    // Tile width with the smallest estimated time: waves of tiles over the SMs, each costing its
+    // width plus a fixed part (pipeline fill, A traffic).  A narrow tile that spills into a second,
+    // mostly empty wave loses to a wider tile that fits in one.
+    int64_t best_cost = 0;
+    for (int cand = 256; cand >= 64; cand >>= 1) {
+      const int64_t tiles = int64_t(args.tiles_m) * ((N + cand - 1) / cand);
+      const int64_t cost = ((tiles + sms - 1) / sms) * (cand + 64);
+      if (bn == 0 || cost < best_cost) { bn = cand; best_cost = cost; }
+    }
   }
   if (kind == KIND_I8 && !b_is_nk && bn < 128) bn = 128;  // an int8 span of N is 128 elements wide
 
+  // Split-K: cut K into ranges so that more CTAs than there are tiles stream B; the partial sums
+  // meet in a stream-ordered workspace.
+  args.splits = 1;
+  args.kb_per_split = 0;
+  args.ws = nullptr;
+  args.counters = nullptr;
+  void* split_ws = nullptr;
+  if (cg == 1 && kind != KIND_TF32 && g_force_splits != 1 && (g_force_bn == 0 || g_force_bn == 256) &&
+      force_bn == 0) {
+    const int bk = 128 / elem;
+    const int64_t num_kb = (K + bk - 1) / bk;
+    const int64_t tiles256 = int64_t(args.tiles_m) * ((N + 255) / 256);
+    // Only on request.  Measured on the fp16 linear layer 4096 -> 11008: with M = 16 three ranges over
+    // 129 CTAs take as long as one 128-wide tile per CTA on 86 CTAs (29 vs 31 us), and with M = 128 the
+    // round trip of the partial sums through the workspace costs more than the extra CTAs bring
+    // (64 vs 33 us), so the automatic choice never splits.
+    int64_t want = g_force_splits > 1 ? g_force_splits : 0;
+    if (want > num_kb) want = num_kb;
+    if (want >= 2) {
+      const int64_t per = (num_kb + want - 1) / want;
+      const int64_t splits = (num_kb + per - 1) / per;  // no empty range
+      if (splits >= 2) {
+        bn = 256;
+        args.splits = int(splits);
+        args.kb_per_split = int(per);
+        const size_t ws_bytes = size_t(tiles256) * splits * BM * 256 * sizeof(uint32_t);
+        const size_t cnt_bytes = (size_t(tiles256) * sizeof(uint32_t) + 255) & ~size_t(255);
+        cudaMemPool_t pool = nullptr;
+        rc = split_k_pool(&pool);
+        if (rc) return rc;
+        B200_CUDA_TRY(cudaMallocFromPoolAsync(&split_ws, cnt_bytes + ws_bytes, pool, stream));
+        B200_CUDA_TRY(cudaMemsetAsync(split_ws, 0, cnt_bytes, stream));
+        args.counters = static_cast<uint32_t*>(split_ws);
+        args.ws = reinterpret_cast<uint32_t*>(static_cast<char*>(split_ws) + cnt_bytes);
+        if (args.store_mode == STORE_TMA) args.store_mode = STORE_VECTOR;  // the finishing item stores from registers
+      }
+    }
+  }
+  rc = launch_kind(kind, epi, bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
+  if (split_ws) {
+    cudaError_t fe = cudaFreeAsync(split_ws, stream);  // stream-ordered: released after the kernel
+    if (rc == B200_OK && fe != cudaSuccess) rc = fail(B200_ERR_CUDA, "cudaFreeAsync: %s", cudaGetErrorString(fe));
+  }
+  return rc;
+}
+
+namespace {
+int launch_kind(int kind, int epi, int bn, int cg, bool b_is_nk, const void* A, const void* B, const GemmArgs& args,
+                int64_t lda, int64_t ldb, cudaStream_t stream) {
   switch (kind) {
     case KIND_I8:
       if (epi == EPI_I32) return launch_bn<KIND_I8, EPI_I32>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
@@ -718,6 +891,7 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   }
   return fail(B200_ERR_BAD_ARGUMENT, "unsupported operand kind %d with epilogue %d", kind, epi);
 }
+}  // namespace
 
 // ------------------------------------------------------------------------------ 3xTF32
 namespace {

@@ -33,6 +33,9 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
                            int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
                            const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream);
 
+// Split-K of the single-CTA tensor-core kernels: 0 = automatic, 1 = never, n = cut K into n ranges.
+int set_split_k(int splits);
+
 // 1 = write C from registers with 16-byte stores instead of staged TMA stores; 0 = automatic.
 int set_store_policy(int register_stores);
 

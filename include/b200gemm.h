@@ -146,6 +146,15 @@ int b200_ipc_close(void* ptr);
  * are 16-byte aligned).  For tests and measurements; results do not depend on it. */
 int b200_set_store_policy(int register_stores);
 
+/* Split-K of the tensor-core kernels.  Products with few output tiles and a long K (a small-M
+ * linear layer) are HBM-bound on the weights; cutting K into ranges lets every SM stream part
+ * of them.  Each range parks its partial sums in a workspace taken from the stream-ordered
+ * allocator (cudaMallocAsync on the call's stream, released after the kernel), and the range
+ * that finishes a tile last adds them in range order and stores C.  0 or 1 = off (the default:
+ * on the shapes measured so far it did not pay), n = n ranges (single-CTA 256-wide tiles).
+ * Integer results are unaffected; floating-point sums are regrouped per range (same tolerance). */
+int b200_set_split_k(int splits);
+
 /* Symmetric absmax quantiser of a row-major fp32 [R, C] matrix to int8 (same shape):
  *   along = 0: scale[r] = max_c |x[r][c]| / 127  (R scales);  along = 1: per column (C scales);
  *   q = clamp(rint(x / scale), -127, 127), ties to even; an all-zero row/column gets scale 1.

@@ -373,7 +373,8 @@ def test_fp32_3xtf32_any_shape(cb, oracle, device, shape, layout_name):
 
 # ------------------------------------------------------------------ W8A8 and the quantiser
 
-@pytest.mark.parametrize("shape", [(33, 80, 64), (300, 520, 1024), (128, 4096, 2048)])
+@pytest.mark.parametrize("shape", [(33, 80, 64), (300, 520, 1024), (128, 4096, 2048), (17, 70, 0), (5, 9000, 0),
+                                   (2048, 12288, 0), (1, 1, 0)])
 def test_quantiser_bit_exact_vs_oracle(cb, oracle, device, shape):
     R, C, _ = shape
     rng = np.random.default_rng(R * C)
@@ -384,6 +385,26 @@ def test_quantiser_bit_exact_vs_oracle(cb, oracle, device, shape):
     for along in (0, 1):
         q, s = cb.quantize_absmax(xd, along)
         want_q, want_s = oracle.quantize_absmax(x, along)
+        assert np.array_equal(s.cpu().numpy(), want_s)
+        assert np.array_equal(q.cpu().numpy(), want_q)
+
+
+def test_quantiser_rounding_ties_match_the_division(cb, oracle, device):
+    """Values whose quotient by the scale sits on (or a few ulps beside) a rounding tie k + 0.5:
+    the kernels' fast quotient must give the same integers as the IEEE division of the oracle."""
+    rng = np.random.default_rng(4)
+    R, C = 64, 4096
+    scale = rng.uniform(0.003, 0.05, R).astype(np.float32)
+    k = rng.integers(-126, 126, (R, C)).astype(np.float32) + 0.5
+    x = (k * scale[:, None]).astype(np.float32)
+    ulps = rng.integers(-3, 4, (R, C)).astype(np.int32)
+    x = (x.view(np.int32) + ulps).view(np.float32)
+    assert np.isfinite(x).all()
+    x[:, 0] = 127.0 * scale            # pins the row maximum, hence the scale
+    xd = to_dev(x, device)
+    for along, xx in ((0, x), (1, np.ascontiguousarray(x.T))):
+        q, s = cb.quantize_absmax(to_dev(xx, device), along)
+        want_q, want_s = oracle.quantize_absmax(xx, along)
         assert np.array_equal(s.cpu().numpy(), want_s)
         assert np.array_equal(q.cpu().numpy(), want_q)
 

@@ -109,6 +109,54 @@ def test_multi_destination_gemm_on_one_gpu(cb, oracle, device, policies, registe
         assert np.array_equal(o.view(torch.int16).cpu().numpy().view(np.uint16), want16)
 
 
+@pytest.fixture
+def split_k(cb):
+    from cudaintro_b200 import capi
+
+    yield capi.set_split_k
+    capi.set_split_k(0)
+
+
+@pytest.mark.parametrize("splits", [0, 1, 2, 5, 16])
+@pytest.mark.parametrize("shape", [(16, 512, 4112), (128, 1040, 2048), (1, 256, 1024), (130, 272, 8192)])
+def test_split_k_int8_and_w8a8_bit_exact(cb, oracle, device, split_k, shape, splits):
+    import torch
+
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K + splits)
+    a = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    b = rng.integers(-127, 128, (K, N)).astype(np.int8)
+    sx = rng.uniform(0.001, 0.02, M).astype(np.float32)
+    sw = rng.uniform(0.001, 0.02, N).astype(np.float32)
+    split_k(splits)
+    ad, bd = to_dev(a, device), to_dev(b, device)
+    for _ in range(2):  # twice: the tile counters must be back at zero after a launch
+        c = cb.gemm_i8_i32(ad, bd)
+        cb.check_device()
+        assert np.array_equal(c.cpu().numpy(), oracle.gemm_i8_i32(a, b, M, N, K))
+    cw = cb.gemm_w8a8_bf16(ad, bd, to_dev(sx, device), to_dev(sw, device))
+    cb.check_device()
+    assert np.array_equal(cw.view(torch.int16).cpu().numpy().view(np.uint16), oracle.gemm_w8a8_bf16(a, b, sx, sw, M, N, K))
+
+
+@pytest.mark.parametrize("M", [16, 128])
+@pytest.mark.parametrize("splits", [0, 1, 3])
+def test_split_k_fp16_linear_layer(cb, device, split_k, M, splits):
+    import torch
+
+    K, N = 4096, 11008
+    g = torch.Generator(device=device).manual_seed(M + splits)
+    x = torch.randn((M, K), device=device, generator=g).to(torch.float16)
+    w = (torch.randn((K, N), device=device, generator=g) * 0.02).to(torch.float16)
+    split_k(splits)
+    y = cb.gemm_f16(x, w)
+    y2 = cb.gemm_f16(x, w)
+    cb.check_device()
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))  # ranges are added in a fixed order
+    ref = cb.gemm_naive(x, w)
+    assert float((y.float() - ref).norm() / ref.norm()) <= 2e-3
+
+
 def test_multi_destination_argument_checks(cb, device):
     import ctypes as C
 
