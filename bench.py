@@ -572,6 +572,14 @@ def side_measurements(device, main_workload):
         out[name] = entry
         del a, b, c, extra
         torch.cuda.empty_cache()
+    # the remaining BASELINE shapes, one kernel each (see cudaintro_b200/measure.py)
+    from cudaintro_b200 import measure
+
+    keep = ("bound", "ms_best", "achieved", "unit", "peak", "frac")
+    for name, res in measure.run_cases(
+            ["int8_4096_colmajor", "linear_m16", "linear_m128", "linear_m1024", "linear_m4096", "fp32_1024_ffma",
+             "fp32_1024_3xtf32", "quantize_rows_8192x8192", "quantize_cols_8192x28672"], reps=5, device=device).items():
+        out[name] = {k: res[k] for k in keep if k in res}
     return out
 
 

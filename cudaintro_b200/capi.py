@@ -13,7 +13,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libb200gemm.so")
 
 ROW_MAJOR, COL_MAJOR_NN, ROW_MAJOR_BT = 0, 1, 2
-F32_FFMA, F32_3XTF32 = 0, 1
+F32_FFMA, F32_3XTF32, F32_TF32 = 0, 1, 2
 I8, F16, BF16, F32, W8A8 = 0, 1, 2, 3, 4
 
 STATUS_NAMES = {0: "OK", 1: "BAD_ARGUMENT", 2: "UNSUPPORTED", 3: "CUDA", 4: "DEVICE_WAIT", 5: "TOO_LARGE"}

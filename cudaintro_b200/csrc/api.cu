@@ -146,6 +146,9 @@ extern "C" int b200_gemm_f32(const float* A, const float* B, float* C, int64_t M
   if (mode == B200_F32_3XTF32)
     return launch_sgemm_3xtf32(static_cast<const float*>(nv.A), static_cast<const float*>(nv.B), C, nv.M, nv.N,
                                nv.K, nv.lda, nv.ldb, nv.ldc, nv.b_is_nk, static_cast<cudaStream_t>(stream));
+  if (mode == B200_F32_TF32)
+    return launch_sgemm_tf32(static_cast<const float*>(nv.A), static_cast<const float*>(nv.B), C, nv.M, nv.N, nv.K,
+                             nv.lda, nv.ldb, nv.ldc, nv.b_is_nk, static_cast<cudaStream_t>(stream));
   return fail(B200_ERR_BAD_ARGUMENT, "unknown fp32 mode %d", mode);
 }
 

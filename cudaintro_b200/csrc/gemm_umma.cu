@@ -88,6 +88,7 @@ struct GemmArgs {
   int kb_per_split;
   uint32_t* ws;
   uint32_t* counters;
+  int single_pass;  // tf32 kind only: 1 = plain fp32 operands, one pass (no split planes)
   const float* row_scale;
   const float* col_scale;
 };
@@ -195,7 +196,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int num_kb = (p.K + T::BK - 1) / T::BK;
   // Split-operand fp32 (3xTF32): A and B each arrive as two stacked planes, low parts on top of
   // high parts, and K is walked three times: lo*hi, then hi*lo, then hi*hi (small terms first).
-  constexpr bool X3 = KIND == KIND_TF32;
+  // With `single_pass` the fp32 operands are read as they are (tf32 keeps the top 19 bits): one walk.
+  const bool X3 = KIND == KIND_TF32 && !p.single_pass;
   const int total_kb = X3 ? 3 * num_kb : num_kb;
 
   if (threadIdx.x == 0) {
@@ -596,7 +598,7 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
     last_dev = dev;
   }
   CUtensorMap ma, mb;
-  constexpr int64_t planes = KIND == KIND_TF32 ? 2 : 1;  // split fp32 operands: low plane, then high plane
+  const int64_t planes = (KIND == KIND_TF32 && !args.single_pass) ? 2 : 1;  // split fp32 operands: low plane, then high plane
   int rc = make_map(&ma, KIND, A, planes * args.M, args.K, lda, T::BK, BM);
   if (rc) return rc;
   if (B_NK)
@@ -657,6 +659,7 @@ int launch_major(bool b_nk, const void* A, const void* B, const GemmArgs& args, 
 int g_force_cg = 0, g_force_bn = 0, g_group_rows = 0;  // 0 = automatic; set through b200_set_tile_policy
 int g_force_store = 0;                                  // 0 = automatic, STORE_VECTOR = register stores
 int g_force_splits = 0;                                 // 0 = automatic, 1 = never split K, n = n ranges
+thread_local bool g_tf32_single_pass_call = false;      // set by launch_sgemm_tf32 around its launch
 
 // Stream-ordered memory pool of the split-K workspaces, one per device.  It keeps what it has
 // handed out before (release threshold at the maximum), so that after the first call an
@@ -797,6 +800,7 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   args.store_mode = !c_aligned16 ? STORE_SCALAR : (g_force_store == STORE_VECTOR ? STORE_VECTOR : STORE_TMA);
   args.row_scale = row_scale;
   args.col_scale = col_scale;
+  args.single_pass = (kind == KIND_TF32 && g_tf32_single_pass_call) ? 1 : 0;
 
   int sms = 0;
   int rc = sm_count_of_current_device(&sms);
@@ -950,6 +954,16 @@ int split_tf32_into(const float* A, const float* B, float* scratch, int64_t M, i
 size_t split_tf32_scratch_floats(int64_t M, int64_t N, int64_t K, bool b_is_nk) {
   const int64_t b_cols = b_is_nk ? K : N, b_rows = b_is_nk ? N : K;
   return size_t(2 * M * ((K + 3) & ~int64_t(3)) + 2 * b_rows * ((b_cols + 3) & ~int64_t(3)));
+}
+
+// fp32 inputs multiplied as tf32 (the tensor cores keep sign, exponent and the top 10 mantissa bits of
+// each operand) with fp32 accumulation: one pass, no scratch.  Relative error of a product ~ 2^-10.
+int launch_sgemm_tf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                      int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream) {
+  g_tf32_single_pass_call = true;
+  int rc = launch_umma_gemm(KIND_TF32, EPI_F32, A, B, C, M, N, K, lda, ldb, ldc, b_is_nk, nullptr, nullptr, 0, stream);
+  g_tf32_single_pass_call = false;
+  return rc;
 }
 
 int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,

@@ -52,6 +52,10 @@ int launch_sgemm_ffma(const float* A, const float* B, float* C, int64_t M, int64
 int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                         int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream);
 
+// Single-pass tf32: fp32 operands read directly by the tensor cores (reduced precision, no scratch).
+int launch_sgemm_tf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                      int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream);
+
 int launch_naive(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                  int64_t lda, int64_t ldb, int64_t ldc, int layout, cudaStream_t stream);
 

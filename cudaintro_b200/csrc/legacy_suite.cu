@@ -5,6 +5,7 @@
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 #include "../../include/gemm_common.h"
 #include "internal.h"
@@ -40,6 +41,17 @@ double suite_seconds() {
 
 constexpr int64_t kDim = 4096;  // M = N = K in all four bodies
 
+// GEMM_SUITE_FP32_MODE = ffma | 3xtf32 | tf32.  The reference asks cuBLAS for tensor-op math on fp32
+// data (quantization/GEMM_fp32.cu:49-54 with the handle in CUBLAS_TENSOR_OP_MATH, main.cu:11), which
+// on this hardware runs at tf32 precision; "tf32" is therefore the like-for-like default, "3xtf32"
+// keeps fp32 accuracy on the tensor cores, "ffma" is exact fp32 arithmetic on the CUDA cores.
+int suite_fp32_mode() {
+  const char* s = std::getenv("GEMM_SUITE_FP32_MODE");
+  if (s && std::strcmp(s, "ffma") == 0) return B200_F32_FFMA;
+  if (s && std::strcmp(s, "3xtf32") == 0) return B200_F32_3XTF32;
+  return B200_F32_TF32;
+}
+
 GemmResult run_suite(const char* name, int dtype, size_t in_elem, size_t out_elem, uint64_t seed_a,
                      uint64_t seed_b) {
   const int64_t M = kDim, N = kDim, K = kDim;
@@ -67,6 +79,7 @@ GemmResult run_suite(const char* name, int dtype, size_t in_elem, size_t out_ele
       break;
   }
 
+  const int fp32_mode = suite_fp32_mode();
   auto gemm = [&]() {
     switch (dtype) {
       case B200_I8:
@@ -76,7 +89,7 @@ GemmResult run_suite(const char* name, int dtype, size_t in_elem, size_t out_ele
       case B200_BF16: return b200_gemm_bf16(a, b, c, M, N, K, M, K, M, B200_COL_MAJOR_NN, nullptr);
       default:
         return b200_gemm_f32(static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c),
-                             M, N, K, M, K, M, B200_COL_MAJOR_NN, B200_F32_FFMA, nullptr);
+                             M, N, K, M, K, M, B200_COL_MAJOR_NN, fp32_mode, nullptr);
     }
   };
 

@@ -180,6 +180,8 @@ def case_f32(n, mode_name):
         ffma_peak = sms * 128 * 2 * 1.965e9 / 1e12  # FP32 lanes x 2 flop x max SM clock
         if mode_name == "F32_FFMA":
             peak, src = ffma_peak, f"{sms} SMs x 128 FP32 lanes x 2 x 1.965 GHz"
+        elif mode_name == "F32_TF32":
+            peak, src = 1125.0, "nominal dense tf32"
         else:
             peak, src = NOMINAL["tf32x3"], "nominal dense tf32 / 3 products per term"
         return {"bound": "fp32 pipe" if mode_name == "F32_FFMA" else "tensor", "ms_median": med, "ms_best": best,
@@ -195,12 +197,15 @@ def case_quantize(R, C, along):
 
         x = _randn((R, C), torch.float32, device, 3)
         med, best = _time(lambda: cb.quantize_absmax(x, along), args.reps, args.warmup)
-        byts = R * C * 5 + 4 * (R if along == 0 else C)  # read fp32 once, write int8 once (+ scales)
+        # Per-row scales: a row is read once (it stays in registers between the two passes) and
+        # written once: 5 B per element.  Per-column scales of a matrix far larger than L2 need the
+        # maxima of all rows before the first element can be quantised: two reads and one write, 9 B.
+        per_elem = 5 if along == 0 else 9
+        byts = R * C * per_elem + 4 * (R if along == 0 else C)
         hbm, _, src = _peaks()
         return {"bound": "hbm", "ms_median": med, "ms_best": best, "achieved": byts / (med * 1e-3) / 1e9, "unit": "GB/s",
                 "peak": hbm, "peak_source": f"{src} HBM copy", "frac": byts / (med * 1e-3) / 1e9 / hbm,
-                "algorithmic_bytes": byts,
-                "note": "algorithmic bytes count x once; the kernels read x twice (absmax pass, quantise pass)"}
+                "algorithmic_bytes": byts, "bytes_per_element": per_elem}
     return run
 
 
@@ -221,6 +226,8 @@ CASES = {
     "fp32_4096_ffma": case_f32(4096, "F32_FFMA"),
     "fp32_1024_3xtf32": case_f32(1024, "F32_3XTF32"),
     "fp32_4096_3xtf32": case_f32(4096, "F32_3XTF32"),
+    "fp32_1024_tf32": case_f32(1024, "F32_TF32"),
+    "fp32_4096_tf32": case_f32(4096, "F32_TF32"),
     "quantize_rows_8192x8192": case_quantize(8192, 8192, 0),
     "quantize_cols_8192x28672": case_quantize(8192, 28672, 1),
 }

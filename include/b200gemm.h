@@ -47,7 +47,13 @@ typedef enum b200_layout {
 
 typedef enum b200_f32_mode {
   B200_F32_FFMA = 0,  /* fp32 FMA on the CUDA cores, k ascending                              */
-  B200_F32_3XTF32 = 1 /* three tf32 tensor-core products per term (hi*hi + hi*lo + lo*hi)     */
+  B200_F32_3XTF32 = 1, /* three tf32 tensor-core products per term (hi*hi + hi*lo + lo*hi):
+                          fp32-level accuracy (relative Frobenius error <= 1e-5)              */
+  B200_F32_TF32 = 2    /* one tf32 tensor-core product per term: operands cut to 10 mantissa bits,
+                          fp32 accumulate (relative Frobenius error <= 2e-3).  This is the
+                          precision class the reference's cublasGemmEx call runs at on this
+                          hardware (CUBLAS_GEMM_DEFAULT_TENSOR_OP under CUBLAS_TENSOR_OP_MATH).
+                          Needs lda, ldb multiples of 4 and 16-byte aligned A, B                */
 } b200_f32_mode;
 
 /* Text of the most recent failure on the calling thread ("" if none). */

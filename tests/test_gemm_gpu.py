@@ -371,6 +371,39 @@ def test_fp32_3xtf32_any_shape(cb, oracle, device, shape, layout_name):
     assert rel_fro(c, truth) <= TOL_F32
 
 
+TOL_TF32 = 2e-3  # one tf32 product per term: operands cut to 10 mantissa bits
+
+
+@pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "COL_MAJOR_NN", "ROW_MAJOR_BT"])
+@pytest.mark.parametrize("shape", [(64, 64, 64), (332, 516, 1000), (1024, 1024, 1024), (4096, 512, 256)])
+def test_fp32_single_pass_tf32(cb, oracle, device, shape, layout_name):
+    layout = getattr(cb, layout_name)
+    M, N, K = shape
+    rng = np.random.default_rng(hash((M, N, K, layout, 1)) & 0xFFFF)
+    sa, sb = storage_shapes(cb, M, N, K, layout)
+    a = rng.uniform(-1, 1, sa).astype(np.float32)
+    b = rng.uniform(-1, 1, sb).astype(np.float32)
+    c = cb.gemm_f32(to_dev(a, device), to_dev(b, device), layout, mode=cb.F32_TF32).cpu().numpy()
+    cb.check_device()
+    if layout == cb.ROW_MAJOR_BT:
+        truth = oracle.gemm_f32(a, np.ascontiguousarray(b.T), M, N, K, acc64=True)
+    else:
+        truth = oracle.gemm_f32(a, b, M, N, K, layout, acc64=True)
+    err = rel_fro(c, truth)
+    assert err <= TOL_TF32
+    assert err > 1e-6  # it really is the reduced-precision path
+
+
+def test_fp32_single_pass_tf32_needs_aligned_rows(cb, device):
+    import torch
+
+    a = torch.zeros((64, 30), device=device)
+    b = torch.zeros((30, 64), device=device)
+    with pytest.raises(cb.B200Error) as e:
+        cb.gemm_f32(a, b, mode=cb.F32_TF32)
+    assert e.value.status == 2
+
+
 # ------------------------------------------------------------------ W8A8 and the quantiser
 
 @pytest.mark.parametrize("shape", [(33, 80, 64), (300, 520, 1024), (128, 4096, 2048), (17, 70, 0), (5, 9000, 0),
