@@ -14,8 +14,12 @@ Workloads
   w8a8        int8 W8A8 linear M=8192, N=28672, K=8192, per-row/per-column scales, bf16 out
 
 On N > 1 GPUs (launched by torchrun, one rank per GPU) the rows of A are split across the ranks,
-B is replicated, every rank computes its [M/N_gpus, N] slab of C in place inside a full [M, N]
-buffer and an NCCL all-gather completes C on every rank; total work is fixed ("strong").
+B is replicated and every rank ends the step with the complete [M, N] C; total work is fixed
+("strong").  By default the GEMM's epilogue stores each finished tile of the rank's slab into
+every rank's copy of C over NVLink (peer memory) and a one-warp marker kernel tells the ranks
+when all slabs have landed; `--gather nccl` runs the plain GEMM followed by an in-place NCCL
+all-gather instead.  Both variants' pieces are timed separately as well (`gemm_phase`,
+`all_gather`, `fused_kernel_ms`).
 
 `value` is whole-job throughput with inputs resident in HBM; `e2e` is the same metric through
 the host-buffer C entry point (pinned host memory, copies inside the timed region).
@@ -67,62 +71,70 @@ def measured_peaks():
 # ----------------------------------------------------------------------------- clock sampling
 
 class ClockSampler:
-    """Samples SM clock and clock-event reasons of one GPU through NVML while a region runs."""
+    """SM clock and clock-event reasons of one GPU, polled by a separate `nvidia-smi` process
+    (every 100 ms) from before the warm-up until after the timed region.
 
-    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
-               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
+    The poller is a process of its own on purpose: NVML queries issued from inside a rank (a
+    sampling thread) take a lock that the rank's own kernel launches need, which slowed an
+    8-rank step by 40 to 130 %.  Only rank 0 polls, and only its own GPU.  Because a timed
+    region can be shorter than one polling period, the caller keeps the same load running,
+    untimed, until the poller has had `min_seconds` of it."""
 
-    def __init__(self, torch_device_index: int):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thread = None
+    FIELDS = ["clocks.sm", "clocks.max.sm", "clocks_event_reasons.hw_slowdown",
+              "clocks_event_reasons.hw_thermal_slowdown", "clocks_event_reasons.sw_thermal_slowdown",
+              "clocks_event_reasons.sw_power_cap"]
+
+    def __init__(self, torch_device_index: int, enabled: bool = True, min_seconds: float = 0.8):
+        self.proc, self.error, self.t_start, self.min_seconds = None, None, None, min_seconds
+        self.out = ""
+        if not enabled:
+            self.error = "clocks are sampled on rank 0 only"
+            return
         try:
-            import pynvml
+            import subprocess
+
             import torch
 
-            pynvml.nvmlInit()
             uuid = str(torch.cuda.get_device_properties(torch_device_index).uuid)
             if not uuid.startswith("GPU-"):
                 uuid = "GPU-" + uuid
-            self._nvml = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
-            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
-        except Exception as e:  # no NVML: the line will say so
-            self._nvml, self._h, self.error = None, None, repr(e)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", uuid, "--query-gpu=" + ",".join(self.FIELDS), "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t_start = time.perf_counter()
+        except Exception as e:
+            self.error = repr(e)
 
-    def _loop(self):
-        nv, h = self._nvml, self._h
-        while not self._stop.is_set():
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
             try:
-                self.samples.append(int(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
-                try:
-                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
-                except Exception:
-                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
-                for bit, name in self.REASONS.items():
-                    if mask & bit:
-                        self.reasons.add(name)
+                self.out, _ = self.proc.communicate(timeout=5)
             except Exception:
-                pass
-            time.sleep(0.002)
-
-    def __enter__(self):
-        if self._nvml is not None:
-            self._thread = threading.Thread(target=self._loop, daemon=True)
-            self._thread.start()
-        return self
-
-    def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
+                self.proc.kill()
+            self.proc = None
 
     def summary(self):
-        if self._nvml is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "error": getattr(self, "error", "no nvml")}
-        s = sorted(self.samples)
-        med = s[len(s) // 2] if s else None
-        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+        if self.error:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "error": self.error}
+        clocks, max_mhz, reasons = [], None, set()
+        for line in self.out.splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) != len(self.FIELDS):
+                continue
+            try:
+                clocks.append(int(parts[0]))
+                max_mhz = int(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:]):
+                if val == "Active":
+                    reasons.add(name)
+        loaded = sorted(clocks[1:] if len(clocks) > 2 else clocks)  # the first sample may predate the load
+        med = loaded[len(loaded) // 2] if loaded else None
+        return {"sm_mhz": med, "sm_max_mhz": max_mhz, "reasons": sorted(reasons), "samples": len(clocks),
+                "how": "nvidia-smi -lms 100 in a separate process, from warm-up to the end of an untimed "
+                       "continuation of the same load"}
 
 
 # ----------------------------------------------------------------------------- workload set-up
@@ -307,6 +319,8 @@ def main():
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N>1: fused = the GEMM epilogue stores each tile into every rank's C over NVLink; "
                          "nccl = GEMM, then NCCL all-gather")
+    ap.add_argument("--clock-sampling", default="rank0", choices=["rank0", "off"],
+                    help="rank0: a separate nvidia-smi process polls rank 0's GPU; off: no clock record")
     ap.add_argument("--register-stores", action="store_true",
                     help="write C straight from registers instead of staged TMA stores (for comparison)")
     args = ap.parse_args()
@@ -371,6 +385,7 @@ def main():
         if not torch.equal(fused.result().view(torch.uint8), sharded.result().view(torch.uint8)):
             raise SystemExit(f"rank {rank}: fused GEMM + all-gather differs from GEMM + NCCL all-gather")
 
+    clocks = ClockSampler(local_rank, enabled=(rank == 0 and args.clock_sampling != "off"))
     for _ in range(max(args.warmup, 3)):
         step()
     cb.check_device()
@@ -378,14 +393,25 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     gemm_ms = 0.0
-    with ClockSampler(local_rank) as clocks:
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
     ms = e0.elapsed_time(e1)
     cb.check_device()
+    # same load, untimed, until the clock poller has covered enough of it (all ranks take part:
+    # a step involves every rank)
+    extra_rounds = torch.zeros(1, dtype=torch.int32, device=device)
+    if rank == 0 and clocks.proc is not None:
+        per_round = max(ms / args.steps * 8 * 1e-3, 1e-4)
+        extra_rounds[0] = int(max(0.0, clocks.min_seconds - (time.perf_counter() - clocks.t_start)) / per_round) + 1
+    if world > 1:
+        dist.broadcast(extra_rounds, src=0)
+    for _ in range(int(extra_rounds.item()) * 8):
+        step()
+    barrier()
+    clocks.stop()
 
     # Average duration of the GEMM kernel alone.  On one GPU a step is exactly one launch, so it
     # is the timed region itself; with a collective in the step it is measured right after.
@@ -415,8 +441,7 @@ def main():
         barrier()
         g0.record()
         for _ in range(args.steps):
-            capi.gemm_multi(what, a, b, fused.slab_ptrs, fused.part.rows, N, K, extra.get("row_scale"),
-                            extra.get("col_scale"))
+            fused.launch(what, a, b, extra.get("row_scale"), extra.get("col_scale"))
         g1.record()
         torch.cuda.synchronize()
         fused_kernel_ms = g0.elapsed_time(g1) / args.steps

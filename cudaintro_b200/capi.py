@@ -44,6 +44,7 @@ SIGNATURES = {
     "b200_set_split_k": (_int, [_int]),
     "b200_gemm_multi": (_int, [_int, _p, _p, C.POINTER(C.c_void_p), _int, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                _p]),
+    "b200_peer_marker": (_int, [C.POINTER(C.c_void_p), _int, _int, C.c_uint32, _p]),
     "b200_peer_alloc": (_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "b200_peer_free": (_int, [_p]),
     "b200_ipc_export": (_int, [_p, _p]),

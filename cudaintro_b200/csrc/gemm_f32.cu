@@ -1,6 +1,6 @@
 // fp32 GEMM on the CUDA cores: C[M,N] = A[M,K] * B with B as [K,N] (N contiguous) or [N,K]
-// (K contiguous).  Register-tiled FFMA: a 256-thread CTA owns a TB x TB tile of C, each thread a
-// (TB/16) x (TB/16) patch held in registers; A and B tiles of 16 k-values are staged through
+// (K contiguous).  Register-tiled FFMA: a 256-thread CTA owns a TBM x TBN tile of C, each thread a
+// (TBM/16) x (TBN/16) patch held in registers; A and B tiles of 16 k-values are staged through
 // double-buffered shared memory (A transposed on the way in so that both operands are read as
 // float4 along the thread's patch).  Every element of C accumulates its products in ascending k
 // into one fp32 accumulator, the order of the reference's CPU loop
@@ -14,6 +14,7 @@ namespace {
 
 constexpr int BKF = 16;
 constexpr int kSgemmThreads = 256;
+constexpr int kPad = 4;  // floats of padding per shared-memory row: keeps float4 alignment, spreads banks
 
 // Loads 4 consecutive k-values of row `r` of a [rows, K] K-contiguous matrix (zero outside).
 template <bool VEC>
@@ -53,30 +54,31 @@ __device__ __forceinline__ float4 load_n4(const float* __restrict__ base, int64_
   return v;
 }
 
-template <int TB, bool B_NK, bool VEC>
-__global__ void __launch_bounds__(kSgemmThreads)
+template <int TBM, int TBN, bool B_NK, bool VEC>
+__global__ void __launch_bounds__(kSgemmThreads, 2)
 sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M,
                   int N, int K, int64_t lda, int64_t ldb, int64_t ldc) {
-  constexpr int TM = TB / 16;           // patch edge per thread (8 for TB = 128, 4 for TB = 64)
-  constexpr int GROUPS = TM / 4;        // float4 groups per patch edge, 64 apart
-  constexpr int A_LOADS = TB * 4 / kSgemmThreads;  // float4 loads of A (and of a K-contiguous B) per thread
-  constexpr int B_LOADS = BKF * (TB / 4) / kSgemmThreads;
+  constexpr int TM = TBM / 16, TN = TBN / 16;  // patch per thread (8 or 4 on each side)
+  constexpr int GM = TM / 4, GN = TN / 4;      // float4 groups per side, 64 rows / columns apart
+  constexpr int A_LOADS = TBM * 4 / kSgemmThreads;  // float4 loads of a K-contiguous operand per thread
+  constexpr int BT_LOADS = TBN * 4 / kSgemmThreads;
+  constexpr int B_LOADS = BKF * (TBN / 4) / kSgemmThreads;
 
-  __shared__ __align__(16) float As[2][BKF][TB];
-  __shared__ __align__(16) float Bs[2][BKF][TB];
+  __shared__ __align__(16) float As[2][BKF][TBM + kPad];
+  __shared__ __align__(16) float Bs[2][BKF][TBN + kPad];
 
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
-  const int m0 = blockIdx.y * TB, n0 = blockIdx.x * TB;
+  const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
 
-  float acc[TM][TM];
+  float acc[TM][TN];
 #pragma unroll
   for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int j = 0; j < TM; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
 
   float4 ra[A_LOADS];
-  float4 rb[B_NK ? A_LOADS : B_LOADS];
+  float4 rb[B_NK ? BT_LOADS : B_LOADS];
 
   auto fetch = [&](int k0) {
 #pragma unroll
@@ -86,15 +88,15 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     }
     if constexpr (B_NK) {
 #pragma unroll
-      for (int l = 0; l < A_LOADS; ++l) {
+      for (int l = 0; l < BT_LOADS; ++l) {
         int idx = tid + l * kSgemmThreads;
         rb[l] = load_k4<VEC>(B, ldb, n0 + (idx >> 2), N, k0 + (idx & 3) * 4, K);
       }
     } else {
 #pragma unroll
       for (int l = 0; l < B_LOADS; ++l) {
-        int idx = tid + l * kSgemmThreads;  // k-row = idx / (TB/4), n-quad = idx % (TB/4)
-        rb[l] = load_n4<VEC>(B, ldb, k0 + idx / (TB / 4), K, n0 + (idx % (TB / 4)) * 4, N);
+        int idx = tid + l * kSgemmThreads;  // k-row = idx / (TBN/4), n-quad = idx % (TBN/4)
+        rb[l] = load_n4<VEC>(B, ldb, k0 + idx / (TBN / 4), K, n0 + (idx % (TBN / 4)) * 4, N);
       }
     }
   };
@@ -110,7 +112,7 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     }
     if constexpr (B_NK) {
 #pragma unroll
-      for (int l = 0; l < A_LOADS; ++l) {
+      for (int l = 0; l < BT_LOADS; ++l) {
         int idx = tid + l * kSgemmThreads;
         int r = idx >> 2, kq = (idx & 3) * 4;
         Bs[buf][kq + 0][r] = rb[l].x;
@@ -122,7 +124,7 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
 #pragma unroll
       for (int l = 0; l < B_LOADS; ++l) {
         int idx = tid + l * kSgemmThreads;
-        *reinterpret_cast<float4*>(&Bs[buf][idx / (TB / 4)][(idx % (TB / 4)) * 4]) = rb[l];
+        *reinterpret_cast<float4*>(&Bs[buf][idx / (TBN / 4)][(idx % (TBN / 4)) * 4]) = rb[l];
       }
     }
   };
@@ -137,18 +139,21 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     if (kb + 1 < num_kb) fetch((kb + 1) * BKF);
 #pragma unroll
     for (int k = 0; k < BKF; ++k) {
-      float a[TM], b[TM];
+      float a[TM], b[TN];
 #pragma unroll
-      for (int g = 0; g < GROUPS; ++g) {
+      for (int g = 0; g < GM; ++g) {
         float4 va = *reinterpret_cast<const float4*>(&As[buf][k][g * 64 + ty * 4]);
-        float4 vb = *reinterpret_cast<const float4*>(&Bs[buf][k][g * 64 + tx * 4]);
         a[g * 4 + 0] = va.x; a[g * 4 + 1] = va.y; a[g * 4 + 2] = va.z; a[g * 4 + 3] = va.w;
+      }
+#pragma unroll
+      for (int g = 0; g < GN; ++g) {
+        float4 vb = *reinterpret_cast<const float4*>(&Bs[buf][k][g * 64 + tx * 4]);
         b[g * 4 + 0] = vb.x; b[g * 4 + 1] = vb.y; b[g * 4 + 2] = vb.z; b[g * 4 + 3] = vb.w;
       }
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TM; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
     }
     if (kb + 1 < num_kb) {
       stash(buf ^ 1);
@@ -162,7 +167,7 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     int m = m0 + (i / 4) * 64 + ty * 4 + (i % 4);
     if (m >= M) continue;
 #pragma unroll
-    for (int g = 0; g < GROUPS; ++g) {
+    for (int g = 0; g < GN; ++g) {
       int n = n0 + g * 64 + tx * 4;
       float* dst = C + int64_t(m) * ldc + n;
       if (vec_out && n + 4 <= N) {
@@ -177,16 +182,28 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
   }
 }
 
-template <int TB, bool B_NK>
+template <int TBM, int TBN, bool B_NK>
 int launch_tb(bool vec, const float* A, const float* B, float* C, int M, int N, int K, int64_t lda,
               int64_t ldb, int64_t ldc, cudaStream_t stream) {
-  dim3 grid((N + TB - 1) / TB, (M + TB - 1) / TB);
+  dim3 grid((N + TBN - 1) / TBN, (M + TBM - 1) / TBM);
+  if (grid.y > 65535) return fail(B200_ERR_TOO_LARGE, "fp32 GEMM: too many row tiles");
   if (vec)
-    sgemm_ffma_kernel<TB, B_NK, true><<<grid, kSgemmThreads, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc);
+    sgemm_ffma_kernel<TBM, TBN, B_NK, true><<<grid, kSgemmThreads, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc);
   else
-    sgemm_ffma_kernel<TB, B_NK, false><<<grid, kSgemmThreads, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc);
+    sgemm_ffma_kernel<TBM, TBN, B_NK, false><<<grid, kSgemmThreads, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
+}
+
+template <bool B_NK>
+int launch_shape(bool vec, const float* A, const float* B, float* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                 int64_t ldc, cudaStream_t stream) {
+  // Largest tile whose grid still covers the machine (two CTAs fit on an SM): 128x128 once there
+  // are at least 148 of them, else 128x64, else 64x64.
+  auto tiles = [&](int tbm, int tbn) { return int64_t((M + tbm - 1) / tbm) * ((N + tbn - 1) / tbn); };
+  if (tiles(128, 128) >= 148) return launch_tb<128, 128, B_NK>(vec, A, B, C, M, N, K, lda, ldb, ldc, stream);
+  if (tiles(128, 64) >= 120) return launch_tb<128, 64, B_NK>(vec, A, B, C, M, N, K, lda, ldb, ldc, stream);
+  return launch_tb<64, 64, B_NK>(vec, A, B, C, M, N, K, lda, ldb, ldc, stream);
 }
 
 }  // namespace
@@ -201,14 +218,8 @@ int launch_sgemm_ffma(const float* A, const float* B, float* C, int64_t M, int64
     return fail(B200_ERR_BAD_ARGUMENT, "a leading dimension is smaller than the row it spans");
   const bool vec = lda % 4 == 0 && ldb % 4 == 0 && reinterpret_cast<uintptr_t>(A) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(B) % 16 == 0;
-  // 128-wide tiles once they fill the machine about twice over, 64-wide tiles below that.
-  const int64_t big_tiles = ((M + 127) / 128) * ((N + 127) / 128);
-  const bool big = big_tiles >= 296;
-  if (big)
-    return b_is_nk ? launch_tb<128, true>(vec, A, B, C, int(M), int(N), int(K), lda, ldb, ldc, stream)
-                   : launch_tb<128, false>(vec, A, B, C, int(M), int(N), int(K), lda, ldb, ldc, stream);
-  return b_is_nk ? launch_tb<64, true>(vec, A, B, C, int(M), int(N), int(K), lda, ldb, ldc, stream)
-                 : launch_tb<64, false>(vec, A, B, C, int(M), int(N), int(K), lda, ldb, ldc, stream);
+  return b_is_nk ? launch_shape<true>(vec, A, B, C, int(M), int(N), int(K), lda, ldb, ldc, stream)
+                 : launch_shape<false>(vec, A, B, C, int(M), int(N), int(K), lda, ldb, ldc, stream);
 }
 
 }  // namespace b200

@@ -1,23 +1,34 @@
 // Tensor-core GEMM for sm_100a: C[M,N] = A[M,K] * B, row-major, for int8 (int32 accumulate),
 // fp16 / bf16 and tf32 (fp32 accumulate).
 //
-// One persistent CTA per SM walks over 128 x BN output tiles.  Inside a CTA the work is split
-// by warp role:
+// Persistent CTAs, one per SM, walk over output tiles.  Inside a CTA the work is split by warp role:
 //   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A tile
 //               (128 rows x 128 bytes of K) and the B tile into a ring of shared-memory stages,
 //               both with the 128-byte swizzle the MMA descriptors expect.
-//   warp 1      MMA issuer: one lane issues tcgen05.mma (M = 128, N = BN, 32 bytes of K per
-//               instruction) from shared memory into an accumulator in tensor memory, and
-//               commits each stage back to the producer.  It also owns the TMEM allocation.
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (32 bytes of K per instruction) from
+//               shared memory into an accumulator in tensor memory, and commits each stage back
+//               to the producer.  It also owns the TMEM allocation.
 //   warps 2-5   epilogue: tcgen05.ld the finished accumulator (one output row per thread),
-//               convert / dequantise and store it with 16-byte stores.
+//               convert / dequantise, and write C either through 128-row x 128-byte tiles staged
+//               in shared memory and stored by TMA (one store per destination buffer: the local
+//               C and, for the sharded product, every peer GPU's copy), or straight from registers.
 // The accumulator is double buffered in TMEM (2 x BN columns), so the epilogue of tile i
 // overlaps the main loop of tile i+1.
+//
+// Two groupings (template parameter CG):
+//   CG = 1  a CTA owns a 128 x BN tile (BN = 256, 128 or 64).
+//   CG = 2  a pair of CTAs (cluster of 2, the two SMs of a TPC) owns a 256 x 256 tile.  Each CTA
+//           stages its own 128 rows of A and its own 128 columns of B; the even-ranked CTA issues
+//           tcgen05.mma.cta_group::2 for both and signals both with multicast commits; each CTA
+//           drains its own 128 accumulator rows.  Loads carry no multicast.
 //
 // B may be given either as [K,N] with N contiguous (the row-major product; also what the
 // reference's column-major cuBLAS call turns into once both sides are transposed) or as [N,K]
 // with K contiguous.  The first form is fed to the tensor cores as an "MN-major" operand: the
-// tile is loaded as BN*elem/128 column spans of 128 bytes, each BK rows tall.
+// tile is loaded as column spans of 128 bytes, each BK rows tall.
+//
+// Optional split-K: a work item is (tile, K range); partial accumulators meet in a workspace and
+// the item that finishes a tile last adds them up in range order.
 //
 // Every mbarrier wait is bounded; a wait that runs out raises a CTA-wide abort flag, all roles
 // drain, tensor memory is freed, and a status word tells the host that the result is invalid.
@@ -1078,4 +1089,64 @@ extern "C" int b200_gemm_f32_3xtf32_static(const float* A, const float* B, float
   if (rc) return rc;
   return launch_umma_gemm(KIND_TF32, EPI_F32, scratch, pb, C, m, n, K, lda_p, ldb_p, ldc, b_is_nk, nullptr, nullptr,
                           0, stream);
+}
+
+// ------------------------------------------------------------------------------ cross-GPU completion marker
+//
+// After a multi-destination GEMM every rank has to learn that all ranks' tiles have landed in its
+// copy of C.  Each rank owns a small flag array in peer-mapped memory, one slot per rank; the
+// marker kernel (one warp, launched on the same stream right after the GEMM) writes this step's
+// number into its slot on every peer and then waits until every slot of its own array has
+// reached that number.  The GEMM's stores precede the flag in stream order and the flag is
+// written with system-scope release, so a rank that sees the flag also sees the tiles.
+// The wait is bounded (two seconds); a rank that gives up records bit 1 of the status word
+// that b200_check_device reports.  The ranks must run on different GPUs.
+namespace b200 {
+namespace {
+
+struct PeerFlagArgs {
+  uint32_t* flags[kMaxDest];  // flags[g]: the flag array (kMaxDest words) that lives on rank g
+  int world;
+  int rank;
+  uint32_t value;
+};
+
+__global__ void peer_marker_kernel(const PeerFlagArgs a) {
+  const int g = threadIdx.x;
+  if (g >= a.world) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flags[g] + a.rank), "r"(a.value) : "memory");
+  const uint32_t* mine = a.flags[a.rank] + g;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t seen;
+  for (;;) {
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    if (int32_t(seen - a.value) >= 0) break;
+    if (global_timer_ns() - t0 > 2000000000ull) {
+      atomicOr(&g_umma_status, 2u);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_peer_marker(void* const* flag_arrays, int world, int rank, uint32_t value, void* stream) {
+  using namespace b200;
+  if (!flag_arrays || world < 1 || world > kMaxDest || rank < 0 || rank >= world)
+    return fail(B200_ERR_BAD_ARGUMENT, "peer marker: bad argument");
+  PeerFlagArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int g = 0; g < world; ++g) {
+    if (!flag_arrays[g]) return fail(B200_ERR_BAD_ARGUMENT, "peer marker: null flag array for rank %d", g);
+    a.flags[g] = static_cast<uint32_t*>(flag_arrays[g]);
+  }
+  a.world = world;
+  a.rank = rank;
+  a.value = value;
+  peer_marker_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  B200_CUDA_TRY(cudaGetLastError());
+  return B200_OK;
 }

@@ -97,17 +97,12 @@ class _RawDeviceBytes:
                                          "strides": None}
 
 
-class FusedShardedGemm:
-    """Row-sharded GEMM whose epilogue writes each finished tile of this rank's slab into EVERY
-    rank's copy of C (peer memory mapped with CUDA IPC), so the gather travels over NVLink while
-    the remaining tiles are still being computed.  A step is one kernel launch plus a one-word
-    all-reduce that tells every rank that all slabs have landed.
+class PeerBuffer:
+    """`nbytes` of device memory on every rank, allocated by the library (``b200_peer_alloc``),
+    exported with CUDA IPC and mapped by all other ranks: ``ptrs[g]`` is rank g's buffer as seen
+    from this process, ``local`` a torch uint8 view of this rank's own."""
 
-    C lives in memory allocated by the library (``b200_peer_alloc``) so that it can be exported
-    to the other ranks; ``c_full`` is a torch view of the local copy.
-    """
-
-    def __init__(self, M: int, N: int, out_dtype, device, group=None):
+    def __init__(self, nbytes: int, device, group=None):
         import ctypes as C
 
         import torch
@@ -115,13 +110,10 @@ class FusedShardedGemm:
 
         from . import capi
 
-        self.dist, self.group, self.capi = dist, group, capi
+        self.capi, self.dist, self.group = capi, dist, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.part = partition_rows(M, self.world, self.rank)
-        self.N = N
-        itemsize = torch.empty((), dtype=out_dtype).element_size()
-        nbytes = self.part.padded_rows * N * itemsize
+        self.nbytes = nbytes
         with torch.cuda.device(device):
             ptr = C.c_void_p()
             capi._check(capi.lib.b200_peer_alloc(nbytes, C.byref(ptr)))
@@ -131,8 +123,7 @@ class FusedShardedGemm:
             handles = [None] * self.world
             if self.world > 1:
                 dist.all_gather_object(handles, handle.raw, group=group)
-            self._imported = []
-            self.ptrs = []
+            self._imported, self.ptrs = [], []
             for r in range(self.world):
                 if r == self.rank:
                     self.ptrs.append(self._local_ptr)
@@ -141,22 +132,74 @@ class FusedShardedGemm:
                     capi._check(capi.lib.b200_ipc_import(handles[r], C.byref(p)))
                     self._imported.append(p.value)
                     self.ptrs.append(p.value)
-        raw = torch.as_tensor(_RawDeviceBytes(self._local_ptr, nbytes), device=device)
-        self.c_full = raw.view(out_dtype).view(self.part.padded_rows, N)
+        self.local = torch.as_tensor(_RawDeviceBytes(self._local_ptr, nbytes), device=device)
+
+    def close(self):
+        for p in self._imported:
+            self.capi.lib.b200_ipc_close(p)
+        self._imported = []
+        if self._local_ptr:
+            self.local = None
+            self.capi.lib.b200_peer_free(self._local_ptr)
+            self._local_ptr = None
+
+
+class FusedShardedGemm:
+    """Row-sharded GEMM whose epilogue writes each finished tile of this rank's slab into EVERY
+    rank's copy of C (peer memory mapped with CUDA IPC), so the gather travels over NVLink while
+    the remaining tiles are still being computed.  A step is the GEMM launch plus a one-warp
+    marker kernel (``b200_peer_marker``): every rank writes the step number into a flag on each
+    peer and waits, with a bound, until all ranks' flags have arrived, which tells it that every
+    slab has landed in its copy of C.
+    """
+
+    def __init__(self, M: int, N: int, out_dtype, device, group=None):
+        import ctypes as C
+
+        import torch
+
+        import torch.distributed as dist
+
+        itemsize = torch.empty((), dtype=out_dtype).element_size()
+
+        self.dist, self.group = dist, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.part = partition_rows(M, self.world, self.rank)
+        self.N = N
+        self._c = PeerBuffer(self.part.padded_rows * N * itemsize, device, group)
+        self._flags = PeerBuffer(256, device, group)
+        self._flags.local.zero_()
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=group)  # every rank's flags are zero before anyone signals
+        self.capi = self._c.capi
+        self.c_full = self._c.local.view(out_dtype).view(self.part.padded_rows, N)
         slab_offset = self.rank * self.part.slot_rows * N * itemsize
-        self.slab_ptrs = [p + slab_offset for p in self.ptrs]
+        # Destination i of this rank is rank (rank + i) % world: the kernel walks its destination list
+        # from a start that rotates with CTA and tile, and with this ordering the ranks, which run in
+        # step with one another, hit different receivers at any moment instead of the same one.
+        self.slab_ptrs = [self._c.ptrs[(self.rank + i) % self.world] + slab_offset for i in range(self.world)]
         r0 = self.rank * self.part.slot_rows
         self.c_slab = self.c_full[r0:r0 + self.part.rows]
-        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self._flag_ptrs = (C.c_void_p * self.world)(*[C.c_void_p(p) for p in self._flags.ptrs])
+        self._step = 0
+
+    def launch(self, what: int, a, b, row_scale=None, col_scale=None):
+        """The multi-destination GEMM alone (no completion marker)."""
+        if self.part.rows > 0:
+            self.capi.gemm_multi(what, a, b, self.slab_ptrs, self.part.rows, self.N, a.shape[1], row_scale, col_scale)
+
+    def mark(self):
+        """Enqueue the cross-rank completion marker for everything launched so far."""
+        if self.world > 1:
+            self._step += 1
+            self.capi._check(self.capi.lib.b200_peer_marker(self._flag_ptrs, self.world, self.rank, self._step,
+                                                            self.capi._stream()))
 
     def step(self, what: int, a, b, row_scale=None, col_scale=None):
-        K = a.shape[1]
-        if self.part.rows > 0:
-            self.capi.gemm_multi(what, a, b, self.slab_ptrs, self.part.rows, self.N, K, row_scale, col_scale)
-        if self.world > 1:
-            # stream-ordered after the kernel on every rank: once it completes here, every rank's
-            # kernel, and with it every remote tile store into this rank's C, has finished
-            self.dist.all_reduce(self._flag, group=self.group)
+        self.launch(what, a, b, row_scale, col_scale)
+        self.mark()
 
     def result(self):
         return self.c_full[: self.part.M]
@@ -167,11 +210,7 @@ class FusedShardedGemm:
         torch.cuda.synchronize()
         if self.world > 1:
             self.dist.barrier(group=self.group)
-        for p in self._imported:
-            self.capi.lib.b200_ipc_close(p)
-        self._imported = []
-        if self._local_ptr:
-            self.c_full = None
-            self.c_slab = None
-            self.capi.lib.b200_peer_free(self._local_ptr)
-            self._local_ptr = None
+        self.c_full = None
+        self.c_slab = None
+        self._flags.close()
+        self._c.close()

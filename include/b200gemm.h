@@ -147,6 +147,15 @@ int b200_ipc_export(void* ptr, void* handle64);
 int b200_ipc_import(const void* handle64, void** ptr);
 int b200_ipc_close(void* ptr);
 
+/* Completion marker for b200_gemm_multi across ranks (one process per GPU, ranks on different
+ * GPUs).  flag_arrays[g] is rank g's flag array: 8 zero-initialised 32-bit words in memory from
+ * b200_peer_alloc, mapped into this process.  The call enqueues a one-warp kernel on `stream`
+ * that writes `value` (use the step number: 1, 2, 3, ...) into slot `rank` of every rank's array
+ * and waits until every slot of its own array has reached `value`, i.e. until every rank's
+ * kernels enqueued before their marker have finished.  The wait gives up after two seconds and
+ * reports through b200_check_device.  No counterpart in the reference. */
+int b200_peer_marker(void* const* flag_arrays, int world, int rank, uint32_t value, void* stream);
+
 /* 1 = the tensor-core kernels write C straight from registers (16-byte stores) instead of
  * staging tiles in shared memory for TMA stores; 0 = automatic (TMA stores whenever C and ldc
  * are 16-byte aligned).  For tests and measurements; results do not depend on it. */
@@ -190,9 +199,10 @@ int b200_gemm_host(int dtype, const void* A, const void* B, void* C, int64_t M, 
                    int layout);
 int b200_host_release(void);
 
-/* Timing helper used by the legacy suite bodies and the bench: runs `iters` back-to-back
- * launches of one of the GEMMs above on `stream` between two CUDA events and returns the
- * elapsed milliseconds in *ms.  row_scale/col_scale are only read for B200_W8A8. */
+/* Timing helper: runs `iters` back-to-back launches of one of the GEMMs above (packed leading
+ * dimensions) on `stream` between two CUDA events, waits for them, and returns the elapsed
+ * milliseconds in *ms together with the outcome of b200_check_device.  row_scale/col_scale are
+ * only read for B200_W8A8. */
 #define B200_W8A8 4
 int b200_time_gemm(int dtype_or_w8a8, const void* A, const void* B, void* C, const float* row_scale,
                    const float* col_scale, int64_t M, int64_t N, int64_t K, int layout, int f32_mode,

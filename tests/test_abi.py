@@ -69,6 +69,31 @@ def test_bad_arguments_are_status_codes_not_crashes(cb):
     assert lib.b200_gemm_f16(one, one, one, 64, 64, 64, 32, 0, 0, 0, None) == 1
 
 
+def test_policy_knobs_and_multi_gpu_entry_points_validate_arguments(cb):
+    from cudaintro_b200 import capi
+
+    lib = capi.lib
+    assert lib.b200_set_tile_policy(3, 0, 0) == 1          # CTA grouping is 0, 1 or 2
+    assert lib.b200_set_tile_policy(2, 128, 0) == 1        # CTA pairs exist for 256-wide tiles only
+    assert lib.b200_set_tile_policy(0, 96, 0) == 1
+    assert lib.b200_set_tile_policy(0, 0, 100) == 1        # group rows: multiple of 256
+    assert lib.b200_set_tile_policy(0, 0, 0) == 0
+    assert lib.b200_set_split_k(-1) == 1 and lib.b200_set_split_k(65) == 1 and lib.b200_set_split_k(0) == 0
+    one = C.c_void_p(16)
+    dests = (C.c_void_p * 9)(*[one] * 9)
+    assert lib.b200_gemm_multi(capi.I8, one, one, dests, 9, None, None, 16, 16, 16, 0, 0, 0, None) == 1
+    assert lib.b200_gemm_multi(capi.I8, one, one, dests, 0, None, None, 16, 16, 16, 0, 0, 0, None) == 1
+    assert lib.b200_gemm_multi(capi.F32, one, one, dests, 1, None, None, 16, 16, 16, 0, 0, 0, None) == 1
+    assert lib.b200_gemm_multi(capi.W8A8, one, one, dests, 1, None, None, 16, 16, 16, 0, 0, 0, None) == 1  # no scales
+    assert lib.b200_peer_marker(dests, 9, 0, 1, None) == 1
+    assert lib.b200_peer_marker(dests, 2, 2, 1, None) == 1
+    assert lib.b200_peer_marker(None, 2, 0, 1, None) == 1
+    assert lib.b200_peer_alloc(0, C.byref(C.c_void_p())) == 1
+    assert lib.b200_ipc_export(None, None) == 1 and lib.b200_ipc_import(None, None) == 1
+    # the allocation-free entry point refuses oversized problems before touching the device
+    assert lib.b200_gemm_f32_3xtf32_static(one, one, one, 4096, 4096, 4096, 0, 0, 0, 0, None) == 5
+
+
 def test_no_cpu_fallback_without_device(cb):
     import torch
 
