@@ -157,6 +157,51 @@ def test_split_k_fp16_linear_layer(cb, device, split_k, M, splits):
     assert float((y.float() - ref).norm() / ref.norm()) <= 2e-3
 
 
+def test_completion_marker_passes_when_all_flags_arrive_and_gives_up_when_one_never_does(cb, oracle, device):
+    """Failure detection without a fault: the marker's wait is bounded.  Here "rank 1" is just a
+    second flag array on the same GPU that nobody ever writes for us, so rank 0's wait for it runs
+    out after its two-second limit; the kernel returns, the status says so, and the context keeps
+    working (a GEMM right after is still bit-exact)."""
+    import ctypes as C
+    import time
+
+    import torch
+    from cudaintro_b200 import capi
+
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # world of one: the only flag it waits for is the one it writes itself
+    solo = torch.zeros(8, dtype=torch.int32, device=device)
+    arr1 = (C.c_void_p * 1)(C.c_void_p(solo.data_ptr()))
+    assert capi.lib.b200_peer_marker(arr1, 1, 0, 1, stream) == 0
+    cb.check_device()
+    assert int(solo[0]) == 1
+
+    mine = torch.zeros(8, dtype=torch.int32, device=device)
+    other = torch.zeros(8, dtype=torch.int32, device=device)
+    arr2 = (C.c_void_p * 2)(C.c_void_p(mine.data_ptr()), C.c_void_p(other.data_ptr()))
+    t0 = time.perf_counter()
+    assert capi.lib.b200_peer_marker(arr2, 2, 0, 1, stream) == 0
+    with pytest.raises(cb.B200Error) as e:
+        cb.check_device()
+    waited = time.perf_counter() - t0
+    assert e.value.status == 4            # B200_ERR_DEVICE_WAIT
+    assert 1.5 < waited < 10.0            # it waited for its bound, not for ever
+    assert int(mine[0]) == 1 and int(other[0]) == 1 and int(mine[1]) == 0
+    cb.check_device()                     # the record was cleared by the failed check
+
+    # a peer that does arrive (its slot in our array already holds the step number): no wait
+    mine[1] = 2
+    assert capi.lib.b200_peer_marker(arr2, 2, 0, 2, stream) == 0
+    cb.check_device()
+
+    rng = np.random.default_rng(1)
+    a = rng.integers(-127, 128, (128, 256)).astype(np.int8)
+    b = rng.integers(-127, 128, (256, 128)).astype(np.int8)
+    c = cb.gemm_i8_i32(to_dev(a, device), to_dev(b, device))
+    cb.check_device()
+    assert np.array_equal(c.cpu().numpy(), oracle.gemm_i8_i32(a, b, 128, 128, 256))
+
+
 def test_multi_destination_argument_checks(cb, device):
     import ctypes as C
 
