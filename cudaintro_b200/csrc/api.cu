@@ -248,6 +248,7 @@ extern "C" int b200_host_release(void) {
 
 extern "C" int b200_set_store_policy(int register_stores) { return set_store_policy(register_stores); }
 extern "C" int b200_set_split_k(int splits) { return set_split_k(splits); }
+extern "C" int b200_set_dependent_launch(int enabled) { return set_dependent_launch(enabled); }
 
 extern "C" int b200_gemm_multi(int what, const void* A, const void* B, void* const* C_list, int n_dest,
                                const float* row_scale, const float* col_scale, int64_t M, int64_t N, int64_t K,

@@ -52,6 +52,8 @@ constexpr int BM = 128;          // rows of C per tile = TMEM lanes
 constexpr int kThreads = 192;    // producer warp, MMA warp, four epilogue warps
 constexpr int kSmemBudget = 227 * 1024;
 
+bool g_use_pdl = true;  // launch the GEMM kernel with programmatic stream serialisation
+
 // CG = 1: one CTA owns a 128 x BN tile.  CG = 2: a pair of CTAs (cluster of 2) owns a 256 x BN tile;
 // each CTA stages its own 128 rows of A and its own BN/2 columns of B, and the even-ranked CTA
 // issues tcgen05.mma.cta_group::2 for both.
@@ -92,11 +94,15 @@ struct GemmArgs {
   int tiles_m, tiles_n;
   int group_m;  // m-tiles per group of the tile order
   int store_mode;  // StoreMode: how the epilogue writes C
-  // Split-K (single CTAs only): K is cut into `splits` ranges of `kb_per_split` k-blocks, one work
+  // Work items.  Items [0, full_items) are whole tiles; every later tile is cut along K into `splits`
+  // ranges of `kb_per_split` k-blocks, one item each (full_items = 0: every tile is cut; splits = 1:
+  // none is).  Cutting the tiles of a partly filled last wave lets the idle SMs take half of each.
+  // Split-K: K is cut into `splits` ranges of `kb_per_split` k-blocks, one work
   // item each; partial accumulators go to `ws` ([tile][split][128][BN] 32-bit words) and the item that
   // finishes a tile last (per `counters[tile]`, zero on entry, reset on exit) adds them up and stores C.
   int splits;
   int kb_per_split;
+  int full_items;
   uint32_t* ws;
   uint32_t* counters;
   int single_pass;  // tf32 kind only: 1 = plain fp32 operands, one pass (no split planes)
@@ -117,6 +123,19 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   int r = t - g * per_group;
   mb = first_m + r % gm;
   nb = r / gm;
+}
+
+struct WorkItem {
+  int tile;    // index in the tile order
+  int split;   // which K range of the tile (0 for a whole tile)
+  int nsplit;  // 1 = whole tile
+  int local;   // index among the cut tiles (workspace and counter slot)
+};
+__device__ __forceinline__ WorkItem decode_item(const GemmArgs& p, int t) {
+  if (t < p.full_items) return WorkItem{t, 0, 1, 0};
+  const int u = t - p.full_items;
+  const int local = u / p.splits;
+  return WorkItem{p.full_items + local, u - local * p.splits, p.splits, local};
 }
 
 // Converts W accumulator columns of one row into output words: W words for 4-byte outputs,
@@ -203,7 +222,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t cta_rank = CG == 2 ? cluster_cta_rank() : 0u;  // 0 = leader of the pair
   const int first_tile = CG == 2 ? int(blockIdx.x >> 1) : int(blockIdx.x);
   const int tile_step = CG == 2 ? int(gridDim.x >> 1) : int(gridDim.x);
-  const int num_tiles = p.tiles_m * p.tiles_n * p.splits;  // work items: (tile, K range)
+  const int num_tiles = p.full_items + (p.tiles_m * p.tiles_n - p.full_items) * p.splits;  // work items
   const int num_kb = (p.K + T::BK - 1) / T::BK;
   // Split-operand fp32 (3xTF32): A and B each arrive as two stacked planes, low parts on top of
   // high parts, and K is walked three times: lo*hi, then hi*lo, then hi*hi (small terms first).
@@ -239,6 +258,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Everything above touched only this CTA's shared and tensor memory.  From here on global memory
+  // is read and written: wait for the kernel this launch was serialised behind (a no-op when the
+  // launch carried no programmatic dependency), and let the next kernel in the stream start its
+  // own set-up as soon as SMs become free.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -248,10 +274,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int it = 0;
       for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
         int mb, nb;
-        const int tile = t / p.splits, split = t - tile * p.splits;
-        tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
-        const int kb_first = split * p.kb_per_split;
-        const int kb_count = p.splits == 1 ? total_kb : min(p.kb_per_split, num_kb - kb_first);
+        const WorkItem wi = decode_item(p, t);
+        tile_coords(wi.tile, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+        const int kb_first = wi.split * p.kb_per_split;
+        const int kb_count = wi.nsplit == 1 ? total_kb : min(p.kb_per_split, num_kb - kb_first);
         // Every other tile walks K backwards: a tile then starts on the k-blocks its predecessor
         // touched last, which are the ones still in L2 (a forward-only sweep over a slab larger
         // than the cache would evict each block just before it is needed again).
@@ -260,7 +286,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int n0 = nb * BN + int(cta_rank) * T::BN_CTA;
         for (int kbt = 0; kbt < kb_count; ++kbt) {
           const int pass = X3 ? kbt / num_kb : 0;
-          const int kb = p.splits > 1 ? kb_first + kbt
+          const int kb = wi.nsplit > 1 ? kb_first + kbt
                                       : (k_reversed ? num_kb - 1 - (kbt - pass * num_kb) : kbt - pass * num_kb);
           const int a_row0 = (X3 && pass != 0) ? p.M : 0;                       // plane 1 = high parts
           const int b_row0 = (X3 && pass != 1) ? (B_NK ? p.N : p.K) : 0;
@@ -317,8 +343,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!mbar_wait_bounded(&acc_empty[ab], acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);
-        const int kb_count =
-            p.splits == 1 ? total_kb : min(p.kb_per_split, num_kb - (t % p.splits) * p.kb_per_split);
+        const WorkItem wi = decode_item(p, t);
+        const int kb_count = wi.nsplit == 1 ? total_kb : min(p.kb_per_split, num_kb - wi.split * p.kb_per_split);
         for (int kb = 0; kb < kb_count; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
@@ -364,8 +390,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int it = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mb, nb;
-      const int tile = t / p.splits, split = t - tile * p.splits;
-      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+      const WorkItem wi = decode_item(p, t);
+      tile_coords(wi.tile, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
       const int ab = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       // One warp polls the barrier; all four then agree on the outcome, so that they always meet at
@@ -382,7 +408,24 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       float rs = 0.f;
       if constexpr (EPI == EPI_W8A8_BF16) rs = row < p.M ? __ldg(p.row_scale + row) : 0.f;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(ab * BN);
-      if (p.store_mode == STORE_TMA) {
+      if (wi.nsplit > 1) {
+        // A K range of a cut tile: park the raw accumulator in the workspace; whoever completes the
+        // tile adds the ranges up in range order (so the result does not depend on who came last).
+        uint32_t* part =
+            p.ws + (((size_t(wi.local) * p.splits + wi.split) * CG + cta_rank) * BM + r_in_tile) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (nb * BN + c * 32 >= p.N) break;
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + uint32_t(c * 32), v);
+          tmem_ld_wait();
+          if (row < p.M) {
+            uint4* dst = reinterpret_cast<uint4*>(part + c * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          }
+        }
+      } else if (p.store_mode == STORE_TMA) {
         // Stage 128 x 128-byte output tiles in shared memory (swizzled like the tensor map expects)
         // and let TMA write them: whole rows per request, clipped at the edges of C, one request
         // per destination buffer.
@@ -421,22 +464,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           ++boxes;
         }
-      } else if (p.splits > 1) {
-        // Split-K: park this K range's raw accumulator in the workspace; whoever completes the tile
-        // adds the ranges up in range order (so the result does not depend on who came last).
-        uint32_t* part = p.ws + ((size_t(tile) * p.splits + split) * BM + r_in_tile) * BN;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          if (nb * BN + c * 32 >= p.N) break;
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + uint32_t(c * 32), v);
-          tmem_ld_wait();
-          if (row < p.M) {
-            uint4* dst = reinterpret_cast<uint4*>(part + c * 32);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          }
-        }
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -455,13 +482,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[ab]), 0));
         else mbar_arrive(&acc_empty[ab]);
       }
-      if (p.splits > 1) {
+      if (wi.nsplit > 1) {
         __threadfence();  // this thread's partial row is visible device-wide before the count goes up
         named_barrier_sync(1, kEpiThreads);
         if (store_thread) {
-          const uint32_t done = atomicAdd(p.counters + tile, 1u);
+          uint32_t* counter = p.counters + wi.local * CG + cta_rank;
+          const uint32_t done = atomicAdd(counter, 1u);
           const bool last = done == uint32_t(p.splits - 1);
-          if (last) p.counters[tile] = 0;  // ready for the next launch
+          if (last) *counter = 0;  // ready for the next launch
           *epi_go = last ? 1u : 0u;
         }
         named_barrier_sync(1, kEpiThreads);
@@ -471,7 +499,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // and every thread has all its loads in flight at once.
           __threadfence();
           const int valid_rows = min(BM, p.M - tile_row0);
-          const uint32_t* base = p.ws + size_t(tile) * p.splits * BM * BN;
+          const uint32_t* base = p.ws + (size_t(wi.local) * p.splits * CG + cta_rank) * BM * BN;
           for (int u = r_in_tile; u < valid_rows * (BN / 8); u += kEpiThreads) {
             const int ur = u / (BN / 8), uc = (u - ur * (BN / 8)) * 8;
             const int n0 = nb * BN + uc;
@@ -480,7 +508,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = 0u;
             for (int sp = 0; sp < p.splits; ++sp) {
-              const uint4* src = reinterpret_cast<const uint4*>(base + (size_t(sp) * BM + ur) * BN + uc);
+              const uint4* src = reinterpret_cast<const uint4*>(base + (size_t(sp) * CG * BM + ur) * BN + uc);
               const uint4 u0 = __ldcg(src), u1 = __ldcg(src + 1);
               const uint32_t in[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
@@ -629,27 +657,36 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
   int sms = 0;
   rc = sm_count_of_current_device(&sms);
   if (rc) return rc;
-  int tiles = args.tiles_m * args.tiles_n * args.splits;  // work items
+  int tiles = args.full_items + (args.tiles_m * args.tiles_n - args.full_items) * args.splits;  // work items
+  // Launch with programmatic stream serialisation: this grid's CTAs may be scheduled, and run their
+  // set-up (barrier init, TMEM allocation, descriptor prefetch), while the kernel before it in the
+  // stream is still draining; they touch no global data before griddepcontrol.wait, which holds them
+  // until that kernel has completed.
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = T::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int nattr = 0;
+  if (g_use_pdl) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
   if constexpr (CG == 2) {
     int pairs = tiles < sms / 2 ? tiles : sms / 2;
-    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(2 * pairs));
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = T::SMEM_BYTES;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mc, args));
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = 2;
+    attr[nattr].val.clusterDim.y = 1;
+    attr[nattr].val.clusterDim.z = 1;
+    ++nattr;
   } else {
-    int grid = tiles < sms ? tiles : sms;
-    kernel<<<grid, kThreads, T::SMEM_BYTES, stream>>>(ma, mb, mc, args);
-    B200_CUDA_TRY(cudaGetLastError());
+    cfg.gridDim = dim3(unsigned(tiles < sms ? tiles : sms));
   }
+  cfg.attrs = attr;
+  cfg.numAttrs = nattr;
+  B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mc, args));
   return B200_OK;
 }
 
@@ -671,6 +708,30 @@ int g_force_cg = 0, g_force_bn = 0, g_group_rows = 0;  // 0 = automatic; set thr
 int g_force_store = 0;                                  // 0 = automatic, STORE_VECTOR = register stores
 int g_force_splits = 0;                                 // 0 = automatic, 1 = never split K, n = n ranges
 thread_local bool g_tf32_single_pass_call = false;      // set by launch_sgemm_tf32 around its launch
+
+// Per-tile counters of the cut tiles: a persistent array per device, zeroed once; every launch takes
+// the next of 64 slots (launches in flight at the same time therefore use different counters) and
+// leaves its counters at zero again, because the item that completes a tile resets its counter.
+constexpr int kCounterSlotWords = 1024;
+constexpr int kCounterSlots = 64;
+int split_k_counters(uint32_t** out) {
+  static std::mutex mu;
+  static uint32_t* base[64] = {nullptr};
+  static unsigned next_slot = 0;
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200_ERR_UNSUPPORTED, "device ordinal %d is beyond the counter table", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void* p = nullptr;
+    const size_t bytes = size_t(kCounterSlots) * kCounterSlotWords * sizeof(uint32_t);
+    B200_CUDA_TRY(cudaMalloc(&p, bytes));
+    B200_CUDA_TRY(cudaMemset(p, 0, bytes));
+    base[dev] = static_cast<uint32_t*>(p);
+  }
+  *out = base[dev] + size_t(next_slot++ % kCounterSlots) * kCounterSlotWords;
+  return B200_OK;
+}
 
 // Stream-ordered memory pool of the split-K workspaces, one per device.  It keeps what it has
 // handed out before (release threshold at the maximum), so that after the first call an
@@ -735,6 +796,11 @@ int set_tile_policy(int cg, int bn, int group_rows) {
 int set_split_k(int splits) {
   if (splits < 0 || splits > 64) return fail(B200_ERR_BAD_ARGUMENT, "split-K: between 0 (automatic) and 64 ranges");
   g_force_splits = splits;
+  return B200_OK;
+}
+
+int set_dependent_launch(int enabled) {
+  g_use_pdl = enabled != 0;
   return B200_OK;
 }
 
@@ -837,43 +903,63 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   }
   if (kind == KIND_I8 && !b_is_nk && bn < 128) bn = 128;  // an int8 span of N is 128 elements wide
 
-  // Split-K: cut K into ranges so that more CTAs than there are tiles stream B; the partial sums
-  // meet in a stream-ordered workspace.
+  // Work items: whole tiles, then (on request only, b200_set_split_k(n >= 2)) tiles cut along K:
+  //  * a product with more tiles than SMs (or SM pairs) whose last wave is less than half full gets
+  //    the tiles of that wave cut into up to n ranges, so that the idle SMs share them;
+  //  * a product with fewer tiles than SMs (single CTAs) gets every tile cut into n ranges.
+  // Partial sums meet in a stream-ordered workspace; the per-tile counters live in a persistent,
+  // self-resetting array (one slot per launch in flight).
+  // Neither pays with the present exchange of partial sums (row-per-thread stores of the raw
+  // accumulator, a fence, a counter, a second pass by the last arriver: about 10 us per cut item).
+  // Measured: int8 4096^3 56 -> 77 us and the fp16 linear layer M = 1024 77 -> 100 us with the last
+  // wave cut; M = 16 / 128 linear layers 31 / 33 us uncut against 29 / 64 us with every tile cut in 3.
   args.splits = 1;
   args.kb_per_split = 0;
   args.ws = nullptr;
   args.counters = nullptr;
   void* split_ws = nullptr;
-  if (cg == 1 && kind != KIND_TF32 && g_force_splits != 1 && (g_force_bn == 0 || g_force_bn == 256) &&
-      force_bn == 0) {
+  {
     const int bk = 128 / elem;
     const int64_t num_kb = (K + bk - 1) / bk;
-    const int64_t tiles256 = int64_t(args.tiles_m) * ((N + 255) / 256);
-    // Only on request.  Measured on the fp16 linear layer 4096 -> 11008: with M = 16 three ranges over
-    // 129 CTAs take as long as one 128-wide tile per CTA on 86 CTAs (29 vs 31 us), and with M = 128 the
-    // round trip of the partial sums through the workspace costs more than the extra CTAs bring
-    // (64 vs 33 us), so the automatic choice never splits.
-    int64_t want = g_force_splits > 1 ? g_force_splits : 0;
+    const int64_t workers = cg == 2 ? sms / 2 : sms;
+    int64_t total = ((M + BM * cg - 1) / (BM * cg)) * ((N + bn - 1) / bn);
+    int64_t full = total, want = 1;
+    const bool asked = kind != KIND_TF32 && g_force_splits > 1 && n_dest == 1;
+    if (asked && total > workers) {
+      const int64_t tail = total % workers;
+      if (tail > 0 && 2 * tail <= workers) {
+        want = workers / tail;
+        if (want > g_force_splits) want = g_force_splits;
+        if (want >= 2) full = total - tail;
+      }
+    } else if (asked && cg == 1 && force_bn == 0 && (g_force_bn == 0 || g_force_bn == 256)) {
+      bn = 256;
+      total = int64_t(args.tiles_m) * ((N + 255) / 256);
+      full = 0;
+      want = g_force_splits;
+    }
     if (want > num_kb) want = num_kb;
-    if (want >= 2) {
+    const int64_t cut = total - full;
+    if (want >= 2 && cut > 0 && cut * cg <= kCounterSlotWords) {
       const int64_t per = (num_kb + want - 1) / want;
       const int64_t splits = (num_kb + per - 1) / per;  // no empty range
       if (splits >= 2) {
-        bn = 256;
         args.splits = int(splits);
         args.kb_per_split = int(per);
-        const size_t ws_bytes = size_t(tiles256) * splits * BM * 256 * sizeof(uint32_t);
-        const size_t cnt_bytes = (size_t(tiles256) * sizeof(uint32_t) + 255) & ~size_t(255);
+        args.full_items = int(full);
+        uint32_t* counters = nullptr;
+        rc = split_k_counters(&counters);
+        if (rc) return rc;
         cudaMemPool_t pool = nullptr;
         rc = split_k_pool(&pool);
         if (rc) return rc;
-        B200_CUDA_TRY(cudaMallocFromPoolAsync(&split_ws, cnt_bytes + ws_bytes, pool, stream));
-        B200_CUDA_TRY(cudaMemsetAsync(split_ws, 0, cnt_bytes, stream));
-        args.counters = static_cast<uint32_t*>(split_ws);
-        args.ws = reinterpret_cast<uint32_t*>(static_cast<char*>(split_ws) + cnt_bytes);
-        if (args.store_mode == STORE_TMA) args.store_mode = STORE_VECTOR;  // the finishing item stores from registers
+        const size_t ws_bytes = size_t(cut) * splits * cg * BM * bn * sizeof(uint32_t);
+        B200_CUDA_TRY(cudaMallocFromPoolAsync(&split_ws, ws_bytes, pool, stream));
+        args.counters = counters;
+        args.ws = static_cast<uint32_t*>(split_ws);
       }
     }
+    if (args.splits == 1) args.full_items = int(total);
   }
   rc = launch_kind(kind, epi, bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
   if (split_ws) {

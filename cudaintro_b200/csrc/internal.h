@@ -36,6 +36,9 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
 // Split-K of the single-CTA tensor-core kernels: 0 = automatic, 1 = never, n = cut K into n ranges.
 int set_split_k(int splits);
 
+// 1 (default) = GEMM kernels are launched with programmatic stream serialisation; 0 = plain launches.
+int set_dependent_launch(int enabled);
+
 // 1 = write C from registers with 16-byte stores instead of staged TMA stores; 0 = automatic.
 int set_store_policy(int register_stores);
 

@@ -161,13 +161,21 @@ int b200_peer_marker(void* const* flag_arrays, int world, int rank, uint32_t val
  * are 16-byte aligned).  For tests and measurements; results do not depend on it. */
 int b200_set_store_policy(int register_stores);
 
-/* Split-K of the tensor-core kernels.  Products with few output tiles and a long K (a small-M
- * linear layer) are HBM-bound on the weights; cutting K into ranges lets every SM stream part
- * of them.  Each range parks its partial sums in a workspace taken from the stream-ordered
- * allocator (cudaMallocAsync on the call's stream, released after the kernel), and the range
- * that finishes a tile last adds them in range order and stores C.  0 or 1 = off (the default:
- * on the shapes measured so far it did not pay), n = n ranges (single-CTA 256-wide tiles).
- * Integer results are unaffected; floating-point sums are regrouped per range (same tolerance). */
+/* 1 (default): the tensor-core kernels are launched with programmatic stream serialisation, so
+ * that a launch's set-up (barrier initialisation, tensor-memory allocation, descriptor prefetch)
+ * overlaps the tail of the kernel before it in the stream; the kernel waits
+ * (griddepcontrol.wait) for that predecessor to complete before it touches global memory, so
+ * stream order is kept.  0: plain launches.  For measurements; results do not depend on it. */
+int b200_set_dependent_launch(int enabled);
+
+/* Split-K of the tensor-core kernels (off by default).  n >= 2 asks for it: a product with fewer
+ * tiles than SMs gets every tile cut along K into n ranges (single-CTA 256-wide tiles); a product
+ * whose last wave of tiles is less than half full gets the tiles of that wave cut into up to n
+ * ranges so that the idle SMs share them.  Each range parks its partial sums in a workspace taken
+ * from the stream-ordered allocator (released after the kernel), and the range that finishes a
+ * tile last adds them in range order and stores C.  0 or 1 = off: on the shapes measured so far
+ * the exchange of partial sums cost more than the extra parallelism brought.  Integer results are
+ * unaffected; floating-point sums are regrouped per range (same tolerance). */
 int b200_set_split_k(int splits);
 
 /* Symmetric absmax quantiser of a row-major fp32 [R, C] matrix to int8 (same shape):

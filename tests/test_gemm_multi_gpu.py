@@ -139,6 +139,35 @@ def test_split_k_int8_and_w8a8_bit_exact(cb, oracle, device, split_k, shape, spl
     assert np.array_equal(cw.view(torch.int16).cpu().numpy().view(np.uint16), oracle.gemm_w8a8_bf16(a, b, sx, sw, M, N, K))
 
 
+@pytest.mark.parametrize("cg", [0, 1])
+@pytest.mark.parametrize("shape", [(4096, 4096, 1024), (4000, 4704, 1152), (2304, 6400, 2048)])
+def test_cut_last_wave_int8_and_w8a8_bit_exact(cb, device, policies, split_k, shape, cg):
+    """Shapes whose tiles leave the last wave of the persistent grid less than half full: with split-K
+    requested those tiles are cut along K (CTA pairs with cg = 0, single CTAs with cg = 1).  Checked
+    in full against the one-thread-per-element kernel, with the cut off (1) and on (2, 4 ranges)."""
+    import torch
+
+    set_tiles, _ = policies
+    M, N, K = shape
+    g = torch.Generator(device=device).manual_seed(M + N + K + cg)
+    a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=device, generator=g)
+    b = torch.randint(-127, 128, (K, N), dtype=torch.int8, device=device, generator=g)
+    rs = torch.rand(M, device=device, generator=g) * 0.01 + 0.001
+    cs = torch.rand(N, device=device, generator=g) * 0.01 + 0.001
+    want = cb.gemm_naive(a, b)
+    want_w = ((want.float() * rs[:, None]) * cs[None, :]).to(torch.bfloat16)
+    set_tiles(cg, 256 if cg else 0, 0)
+    for mode in (1, 2, 4):
+        split_k(mode)
+        for _ in range(2):  # twice: the counters of the cut tiles must be back at zero
+            c = cb.gemm_i8_i32(a, b)
+            cb.check_device()
+            assert torch.equal(c, want), (mode,)
+        cw = cb.gemm_w8a8_bf16(a, b, rs, cs)
+        cb.check_device()
+        assert torch.equal(cw.view(torch.int16), want_w.view(torch.int16)), (mode,)
+
+
 @pytest.mark.parametrize("M", [16, 128])
 @pytest.mark.parametrize("splits", [0, 1, 3])
 def test_split_k_fp16_linear_layer(cb, device, split_k, M, splits):
