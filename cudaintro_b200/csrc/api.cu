@@ -69,15 +69,36 @@ int gemm_tensor(int kind, int epi, const void* A, const void* B, void* C, int64_
                           cs, 0, static_cast<cudaStream_t>(stream));
 }
 
-// Device workspace of the *_host entry point (one per process, grows on demand).
+// Device workspace of the *_host entry point (one per process, grows on demand): the three
+// matrices, one stream per direction of travel plus one for the kernels, and the events that chain
+// them chunk by chunk.
+constexpr int kHostChunks = 16;
 struct HostWorkspace {
   std::mutex mu;
   void* dA = nullptr;
   void* dB = nullptr;
   void* dC = nullptr;
   size_t capA = 0, capB = 0, capC = 0;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;      // kernels
+  cudaStream_t in_stream = nullptr;   // host -> device copies
+  cudaStream_t out_stream = nullptr;  // device -> host copies
+  cudaEvent_t whole_in = nullptr;     // the operand that is needed whole has arrived
+  cudaEvent_t chunk_in[kHostChunks] = {nullptr};
+  cudaEvent_t chunk_done[kHostChunks] = {nullptr};
 } g_ws;
+
+int host_streams_ready() {
+  if (g_ws.stream) return B200_OK;
+  B200_CUDA_TRY(cudaStreamCreateWithFlags(&g_ws.stream, cudaStreamNonBlocking));
+  B200_CUDA_TRY(cudaStreamCreateWithFlags(&g_ws.in_stream, cudaStreamNonBlocking));
+  B200_CUDA_TRY(cudaStreamCreateWithFlags(&g_ws.out_stream, cudaStreamNonBlocking));
+  B200_CUDA_TRY(cudaEventCreateWithFlags(&g_ws.whole_in, cudaEventDisableTiming));
+  for (int i = 0; i < kHostChunks; ++i) {
+    B200_CUDA_TRY(cudaEventCreateWithFlags(&g_ws.chunk_in[i], cudaEventDisableTiming));
+    B200_CUDA_TRY(cudaEventCreateWithFlags(&g_ws.chunk_done[i], cudaEventDisableTiming));
+  }
+  return B200_OK;
+}
 
 int grow(void** p, size_t* cap, size_t need) {
   if (*cap >= need) return B200_OK;
@@ -206,10 +227,17 @@ extern "C" int b200_time_gemm(int what, const void* A, const void* B, void* C, c
   return rc;
 }
 
+// Host buffers in, host buffers out.  The product is cut into up to 16 slabs along the dimension in
+// which both an input and the output are contiguous (rows of A and C for the row-major layouts,
+// columns of B and C for the column-major one).  The other operand goes up whole; then slab i + 1 is
+// on its way up while slab i is multiplied and slab i - 1 of the result is on its way down, so the
+// call takes about as long as its host-to-device traffic alone.
 extern "C" int b200_gemm_host(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                               int layout) {
   if (!A || !B || !C) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
   if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
+  if (layout != B200_ROW_MAJOR && layout != B200_COL_MAJOR_NN && layout != B200_ROW_MAJOR_BT)
+    return fail(B200_ERR_BAD_ARGUMENT, "unknown layout %d", layout);
   size_t in_elem, out_elem;
   switch (dtype) {
     case B200_I8: in_elem = 1; out_elem = 4; break;
@@ -218,18 +246,58 @@ extern "C" int b200_gemm_host(int dtype, const void* A, const void* B, void* C, 
     default: return fail(B200_ERR_BAD_ARGUMENT, "unknown dtype %d", dtype);
   }
   std::lock_guard<std::mutex> lock(g_ws.mu);
-  if (!g_ws.stream) B200_CUDA_TRY(cudaStreamCreateWithFlags(&g_ws.stream, cudaStreamNonBlocking));
+  int rc = host_streams_ready();
+  if (rc) return rc;
   const size_t bytesA = size_t(M) * K * in_elem, bytesB = size_t(K) * N * in_elem, bytesC = size_t(M) * N * out_elem;
-  int rc;
   if ((rc = grow(&g_ws.dA, &g_ws.capA, bytesA))) return rc;
   if ((rc = grow(&g_ws.dB, &g_ws.capB, bytesB))) return rc;
   if ((rc = grow(&g_ws.dC, &g_ws.capC, bytesC))) return rc;
-  B200_CUDA_TRY(cudaMemcpyAsync(g_ws.dA, A, bytesA, cudaMemcpyHostToDevice, g_ws.stream));
-  B200_CUDA_TRY(cudaMemcpyAsync(g_ws.dB, B, bytesB, cudaMemcpyHostToDevice, g_ws.stream));
-  rc = dispatch(dtype, g_ws.dA, g_ws.dB, g_ws.dC, nullptr, nullptr, M, N, K, layout, B200_F32_FFMA, g_ws.stream);
+
+  const bool col = layout == B200_COL_MAJOR_NN;
+  const char* whole_src = static_cast<const char*>(col ? A : B);
+  char* whole_dst = static_cast<char*>(col ? g_ws.dA : g_ws.dB);
+  const size_t whole_bytes = col ? bytesA : bytesB;
+  const char* slab_src = static_cast<const char*>(col ? B : A);
+  char* slab_dst = static_cast<char*>(col ? g_ws.dB : g_ws.dA);
+  const int64_t units = col ? N : M;                                 // rows of A / columns of B
+  const size_t in_unit = size_t(K) * in_elem;                        // bytes of one of them
+  const size_t out_unit = size_t(col ? M : N) * out_elem;            // bytes of the matching line of C
+  // Slabs of a multiple of 256 units (the tallest tile), at least 512, at most 16 of them.
+  int64_t per = (units + kHostChunks - 1) / kHostChunks;
+  per = (per + 255) / 256 * 256;
+  if (per < 512) per = 512;
+
+  B200_CUDA_TRY(cudaMemcpyAsync(whole_dst, whole_src, whole_bytes, cudaMemcpyHostToDevice, g_ws.in_stream));
+  B200_CUDA_TRY(cudaEventRecord(g_ws.whole_in, g_ws.in_stream));
+  B200_CUDA_TRY(cudaStreamWaitEvent(g_ws.stream, g_ws.whole_in, 0));
+  int i = 0;
+  for (int64_t u0 = 0; u0 < units; u0 += per, ++i) {
+    const int64_t n_units = units - u0 < per ? units - u0 : per;
+    B200_CUDA_TRY(cudaMemcpyAsync(slab_dst + u0 * in_unit, slab_src + u0 * in_unit, size_t(n_units) * in_unit,
+                                  cudaMemcpyHostToDevice, g_ws.in_stream));
+    B200_CUDA_TRY(cudaEventRecord(g_ws.chunk_in[i], g_ws.in_stream));
+    B200_CUDA_TRY(cudaStreamWaitEvent(g_ws.stream, g_ws.chunk_in[i], 0));
+    char* c_dev = static_cast<char*>(g_ws.dC) + u0 * out_unit;
+    if (col)
+      rc = dispatch(dtype, g_ws.dA, slab_dst + u0 * in_unit, c_dev, nullptr, nullptr, M, n_units, K, layout,
+                    B200_F32_FFMA, g_ws.stream);
+    else
+      rc = dispatch(dtype, slab_dst + u0 * in_unit, g_ws.dB, c_dev, nullptr, nullptr, n_units, N, K, layout,
+                    B200_F32_FFMA, g_ws.stream);
+    if (rc) break;
+    B200_CUDA_TRY(cudaEventRecord(g_ws.chunk_done[i], g_ws.stream));
+    B200_CUDA_TRY(cudaStreamWaitEvent(g_ws.out_stream, g_ws.chunk_done[i], 0));
+    B200_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(C) + u0 * out_unit, c_dev, size_t(n_units) * out_unit,
+                                  cudaMemcpyDeviceToHost, g_ws.out_stream));
+  }
+  // Everything issued must have finished before the buffers are reused or an error is returned.
+  cudaError_t e_in = cudaStreamSynchronize(g_ws.in_stream);
+  cudaError_t e_out = cudaStreamSynchronize(g_ws.out_stream);
+  const int dev_rc = b200_check_device(g_ws.stream);
   if (rc) return rc;
-  B200_CUDA_TRY(cudaMemcpyAsync(C, g_ws.dC, bytesC, cudaMemcpyDeviceToHost, g_ws.stream));
-  return b200_check_device(g_ws.stream);
+  if (e_in != cudaSuccess) return fail(B200_ERR_CUDA, "host-to-device copies: %s", cudaGetErrorString(e_in));
+  if (e_out != cudaSuccess) return fail(B200_ERR_CUDA, "device-to-host copies: %s", cudaGetErrorString(e_out));
+  return dev_rc;
 }
 
 extern "C" int b200_host_release(void) {
@@ -239,8 +307,17 @@ extern "C" int b200_host_release(void) {
   if (g_ws.dC) cudaFree(g_ws.dC);
   g_ws.dA = g_ws.dB = g_ws.dC = nullptr;
   g_ws.capA = g_ws.capB = g_ws.capC = 0;
-  if (g_ws.stream) cudaStreamDestroy(g_ws.stream);
-  g_ws.stream = nullptr;
+  if (g_ws.stream) {
+    cudaStreamDestroy(g_ws.stream);
+    cudaStreamDestroy(g_ws.in_stream);
+    cudaStreamDestroy(g_ws.out_stream);
+    cudaEventDestroy(g_ws.whole_in);
+    for (int i = 0; i < kHostChunks; ++i) {
+      cudaEventDestroy(g_ws.chunk_in[i]);
+      cudaEventDestroy(g_ws.chunk_done[i]);
+    }
+  }
+  g_ws.stream = g_ws.in_stream = g_ws.out_stream = nullptr;
   return B200_OK;
 }
 

@@ -199,10 +199,14 @@ typedef enum b200_dtype { B200_I8 = 0, B200_F16 = 1, B200_BF16 = 2, B200_F32 = 3
 int b200_gemm_naive(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream);
 
-/* Same products with HOST buffers: copies A and B to the device, runs the kernel, copies C
+/* Same products with HOST buffers: copies A and B to the device, runs the kernels, copies C
  * back, and returns after the result is in `C`.  `dtype` selects the entry point above
- * (B200_I8 -> int32 out, B200_F16 / B200_BF16 -> 16-bit out, B200_F32 -> FFMA).  Device
- * workspace is kept between calls and grows as needed; b200_host_release() frees it. */
+ * (B200_I8 -> int32 out, B200_F16 / B200_BF16 -> 16-bit out, B200_F32 -> FFMA).  The operand
+ * every output line needs goes up whole (B; A for the column-major layout); the other one travels
+ * in up to 16 slabs of rows (columns), each multiplied as soon as it has arrived and copied back
+ * while the next is on its way, so with pinned buffers the call costs about its host-to-device
+ * traffic.  Device workspace, three streams and their events are kept between calls and grow as
+ * needed; b200_host_release() frees them.  Calls are serialised by a lock. */
 int b200_gemm_host(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                    int layout);
 int b200_host_release(void);

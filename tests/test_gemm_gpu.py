@@ -504,6 +504,40 @@ def test_host_buffer_entry_point(cb, oracle):
     capi.lib.b200_host_release()
 
 
+@pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "COL_MAJOR_NN", "ROW_MAJOR_BT"])
+def test_host_buffer_entry_point_in_several_slabs(cb, oracle, device, layout_name):
+    """2000 lines of the slab dimension: four slabs of 512 (the last one ragged) travel up, through
+    the kernels and down again on three streams.  int8 bit-exact against the oracle; bf16 equal to
+    the device-buffer call to rounding.
+    Called twice: the second call reuses the workspace while nothing of the first is in flight."""
+    import torch
+    from cudaintro_b200 import capi
+
+    layout = getattr(cb, layout_name)
+    M, N, K = (2000, 656, 768) if layout != cb.COL_MAJOR_NN else (656, 2000, 768)
+    if layout == cb.COL_MAJOR_NN:
+        M = 656 // 16 * 16 + 16
+    rng = np.random.default_rng(7 + layout)
+    sa, sb = storage_shapes(cb, M, N, K, layout)
+    sc = (N, M) if layout == cb.COL_MAJOR_NN else (M, N)
+    a = rng.integers(-127, 128, sa).astype(np.int8)
+    b = rng.integers(-127, 128, sb).astype(np.int8)
+    want = oracle_i8(oracle, cb, a, b, M, N, K, layout)
+    for _ in range(2):
+        c = np.full(sc, -7, dtype=np.int32)
+        cb.gemm_host(capi.I8, a, b, c, M, N, K, layout)
+        assert np.array_equal(c, want)
+    a16 = oracle.f32_to_bf16_bits(rng.standard_normal(sa).astype(np.float32))
+    b16 = oracle.f32_to_bf16_bits(rng.standard_normal(sb).astype(np.float32))
+    want16 = cb.gemm_bf16(to_dev(a16.view(np.int16), device, torch.bfloat16),
+                          to_dev(b16.view(np.int16), device, torch.bfloat16), layout)
+    c16 = np.zeros(sc, dtype=np.uint16)
+    cb.gemm_host(capi.BF16, a16, b16, c16, M, N, K, layout)
+    got = torch.from_numpy(c16.view(np.int16)).view(torch.bfloat16).float().numpy()
+    assert rel_fro(got, want16.float().cpu().numpy()) <= 1e-3
+    capi.lib.b200_host_release()
+
+
 def test_suite_entry_points_keep_the_reference_protocol(cb, device, monkeypatch):
     """run_gemm_* (quantization/gemm_common.h:64-67) through their C++ symbols: name, iteration
     count in multiples of 256, and the reference's TFLOP/s formula (GEMM_int8.cu:80-84)."""
@@ -595,3 +629,44 @@ def test_w8a8_tile_policies_agree_bit_for_bit(cb, oracle, device, policy):
         c = cb.gemm_w8a8_bf16(to_dev(qx, device), to_dev(qw, device), to_dev(sx, device), to_dev(sw, device))
         cb.check_device()
         assert np.array_equal(c.view(torch.int16).cpu().numpy().view(np.uint16), want), (cg, bn)
+
+
+@pytest.mark.parametrize("M", [1, 16, 32, 33, 64, 65])
+def test_skinny_products_on_wide_tiles(cb, oracle, device, policy, M):
+    """A handful of rows against a wide weight matrix on 128-wide tiles (the decode-shape path): most
+    of the 128 accumulator rows of every tile are padding; nothing of them may reach C, and the rows
+    that count must still be exact.  K is long enough for the stage ring to wrap several times."""
+    import torch
+
+    N, K = 528, 2176  # 17 / 34 k-blocks
+    rng = np.random.default_rng(4000 + M)
+    policy(1, 128)
+    # int8, both B layouts, bit-exact
+    a = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    b = rng.integers(-127, 128, (K, N)).astype(np.int8)
+    want = oracle.gemm_i8_i32(a, b, M, N, K, oracle.ROW_MAJOR)
+    for layout, bb in ((cb.ROW_MAJOR, b), (cb.ROW_MAJOR_BT, np.ascontiguousarray(b.T))):
+        c = cb.gemm_i8_i32(to_dev(a, device), to_dev(bb, device), layout)
+        cb.check_device()
+        assert np.array_equal(c.cpu().numpy(), want), layout
+    # W8A8 -> bf16, bit-exact
+    qx, sx = oracle.quantize_absmax(rng.standard_normal((M, K)).astype(np.float32), 0)
+    qw, sw = oracle.quantize_absmax(rng.standard_normal((K, N)).astype(np.float32), 1)
+    c = cb.gemm_w8a8_bf16(to_dev(qx, device), to_dev(qw, device), to_dev(sx, device), to_dev(sw, device))
+    cb.check_device()
+    assert np.array_equal(c.view(torch.int16).cpu().numpy().view(np.uint16),
+                          oracle.gemm_w8a8_bf16(qx, qw, sx, sw, M, N, K))
+    # fp16 and bf16 within their tolerances, and finite everywhere
+    af = rng.standard_normal((M, K)).astype(np.float32)
+    bf = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    for is_bf16, tol in ((True, TOL_BF16), (False, TOL_F16)):
+        conv = oracle.f32_to_bf16_bits if is_bf16 else (lambda x: x.astype(np.float16).view(np.uint16))
+        dt = torch.bfloat16 if is_bf16 else torch.float16
+        a16, b16 = conv(af), conv(bf)
+        fn = cb.gemm_bf16 if is_bf16 else cb.gemm_f16
+        c = fn(to_dev(a16.view(np.int16), device, dt), to_dev(b16.view(np.int16), device, dt), cb.ROW_MAJOR)
+        cb.check_device()
+        _, o32 = oracle.gemm_h16(a16, b16, M, N, K, is_bf16)
+        got = c.float().cpu().numpy()
+        assert np.isfinite(got).all()
+        assert rel_fro(got, o32) <= tol, is_bf16
