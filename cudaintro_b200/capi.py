@@ -38,6 +38,7 @@ SIGNATURES = {
     "b200_fill_bf16": (_int, [_p, _i64, C.c_uint64, C.c_float, C.c_float, _p]),
     "b200_fill_f32": (_int, [_p, _i64, C.c_uint64, C.c_float, C.c_float, _p]),
     "b200_gemm_naive": (_int, [_int, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
+    "b200_linear": (_int, [_int, _p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _int, _p]),
     "b200_gemm_host": (_int, [_int, _p, _p, _p, _i64, _i64, _i64, _int]),
     "b200_host_release": (_int, []),
     "b200_set_store_policy": (_int, [_int]),
@@ -187,6 +188,29 @@ def _code(dtype):
     if _DTYPE_CODE is None:
         _DTYPE_CODE = {torch.int8: I8, torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
     return _DTYPE_CODE[dtype]
+
+
+LINEAR_RELU, LINEAR_BIAS_FIRST = 1, 2
+
+
+def linear(x, w, bias=None, w_layout=ROW_MAJOR_BT, relu=False, bias_first=False, mode=F32_FFMA, out=None):
+    """Fused fully connected layer: act(x @ W^T + bias) for W [out, in] (ROW_MAJOR_BT, the default) or
+    act(x @ W + bias) for W [in, out] (ROW_MAJOR).  x, W: fp32, fp16 or bf16 CUDA tensors; bias fp32."""
+    import torch
+
+    assert x.dtype == w.dtype and x.dim() == 2 and w.dim() == 2
+    batch, in_f = x.shape
+    out_f = w.shape[0] if w_layout == ROW_MAJOR_BT else w.shape[1]
+    assert (w.shape[1] if w_layout == ROW_MAJOR_BT else w.shape[0]) == in_f
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == out_f
+    if out is None:
+        out = torch.empty((batch, out_f), dtype=x.dtype, device=x.device)
+    flags = (LINEAR_RELU if relu else 0) | (LINEAR_BIAS_FIRST if bias_first else 0)
+    with torch.cuda.device(x.device):
+        _check(lib.b200_linear(_code(x.dtype), x.data_ptr(), w.data_ptr(), 0 if bias is None else bias.data_ptr(),
+                               out.data_ptr(), batch, in_f, out_f, w_layout, flags, mode, _stream()))
+    return out
 
 
 def gemm_naive(a, b, layout=ROW_MAJOR):

@@ -173,6 +173,42 @@ extern "C" int b200_gemm_f32(const float* A, const float* B, float* C, int64_t M
   return fail(B200_ERR_BAD_ARGUMENT, "unknown fp32 mode %d", mode);
 }
 
+extern "C" int b200_linear(int dtype, const void* X, const void* W, const float* bias, void* Y, int64_t batch,
+                           int64_t in_features, int64_t out_features, int w_layout, int flags, int f32_mode,
+                           void* stream_) {
+  if (!X || !W || !Y) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
+  if (batch <= 0 || in_features <= 0 || out_features <= 0)
+    return fail(B200_ERR_BAD_ARGUMENT, "batch and feature counts must be positive");
+  if (w_layout != B200_ROW_MAJOR && w_layout != B200_ROW_MAJOR_BT)
+    return fail(B200_ERR_BAD_ARGUMENT, "weights are [in, out] (B200_ROW_MAJOR) or [out, in] (B200_ROW_MAJOR_BT)");
+  if (flags & ~(B200_LINEAR_RELU | B200_LINEAR_BIAS_FIRST)) return fail(B200_ERR_BAD_ARGUMENT, "unknown flags 0x%x", flags);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const bool w_is_out_in = w_layout == B200_ROW_MAJOR_BT;
+  const int64_t M = batch, N = out_features, K = in_features;
+  const int64_t ldw = w_is_out_in ? K : N;
+  Tail tail;
+  tail.bias = bias;
+  tail.flags = flags;
+  switch (dtype) {
+    case B200_F32: {
+      const float* x = static_cast<const float*>(X);
+      const float* w = static_cast<const float*>(W);
+      float* y = static_cast<float*>(Y);
+      if (f32_mode == B200_F32_FFMA) return launch_sgemm_ffma(x, w, y, M, N, K, K, ldw, N, w_is_out_in, stream, tail);
+      if (f32_mode == B200_F32_3XTF32) return launch_sgemm_3xtf32(x, w, y, M, N, K, K, ldw, N, w_is_out_in, stream, tail);
+      if (f32_mode == B200_F32_TF32) return launch_sgemm_tf32(x, w, y, M, N, K, K, ldw, N, w_is_out_in, stream, tail);
+      return fail(B200_ERR_BAD_ARGUMENT, "unknown fp32 mode %d", f32_mode);
+    }
+    case B200_F16:
+      return launch_umma_gemm(KIND_F16, EPI_F16, X, W, Y, M, N, K, K, ldw, N, w_is_out_in, nullptr, nullptr, 0, stream,
+                              tail);
+    case B200_BF16:
+      return launch_umma_gemm(KIND_BF16, EPI_BF16, X, W, Y, M, N, K, K, ldw, N, w_is_out_in, nullptr, nullptr, 0,
+                              stream, tail);
+  }
+  return fail(B200_ERR_BAD_ARGUMENT, "b200_linear: dtype %d is not a floating-point type", dtype);
+}
+
 extern "C" int b200_gemm_naive(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N,
                                int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream) {
   if (layout != B200_ROW_MAJOR && layout != B200_COL_MAJOR_NN && layout != B200_ROW_MAJOR_BT)

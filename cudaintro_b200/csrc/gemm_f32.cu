@@ -57,7 +57,7 @@ __device__ __forceinline__ float4 load_n4(const float* __restrict__ base, int64_
 template <int TBM, int TBN, bool B_NK, bool VEC>
 __global__ void __launch_bounds__(kSgemmThreads, 2)
 sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M,
-                  int N, int K, int64_t lda, int64_t ldb, int64_t ldc) {
+                  int N, int K, int64_t lda, int64_t ldb, int64_t ldc, const float* __restrict__ bias, int flags) {
   constexpr int TM = TBM / 16, TN = TBN / 16;  // patch per thread (8 or 4 on each side)
   constexpr int GM = TM / 4, GN = TN / 4;      // float4 groups per side, 64 rows / columns apart
   constexpr int A_LOADS = TBM * 4 / kSgemmThreads;  // float4 loads of a K-contiguous operand per thread
@@ -71,11 +71,19 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
   const int tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
 
+  // Fully connected layer: the sum of column n either starts from bias[n] or gets it added at the
+  // end; both orders exist in the reference and round differently.
+  const bool bias_first = bias != nullptr && (flags & B200_LINEAR_BIAS_FIRST) != 0;
+  const bool bias_last = bias != nullptr && !bias_first;
+  const bool relu = (flags & B200_LINEAR_RELU) != 0;
   float acc[TM][TN];
 #pragma unroll
-  for (int i = 0; i < TM; ++i)
+  for (int j = 0; j < TN; ++j) {
+    const int n = n0 + (j / 4) * 64 + tx * 4 + (j % 4);
+    const float start = (bias_first && n < N) ? __ldg(bias + n) : 0.f;
 #pragma unroll
-    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    for (int i = 0; i < TM; ++i) acc[i][j] = start;
+  }
 
   float4 ra[A_LOADS];
   float4 rb[B_NK ? BT_LOADS : B_LOADS];
@@ -161,6 +169,18 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     }
   }
 
+  if (bias_last || relu) {
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int n = n0 + (j / 4) * 64 + tx * 4 + (j % 4);
+      const float add = (bias_last && n < N) ? __ldg(bias + n) : 0.f;
+#pragma unroll
+      for (int i = 0; i < TM; ++i) {
+        float v = bias_last ? acc[i][j] + add : acc[i][j];
+        acc[i][j] = relu ? fmaxf(0.0f, v) : v;
+      }
+    }
+  }
   const bool vec_out = VEC && (ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(C) % 16 == 0);
 #pragma unroll
   for (int i = 0; i < TM; ++i) {
@@ -184,32 +204,34 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
 
 template <int TBM, int TBN, bool B_NK>
 int launch_tb(bool vec, const float* A, const float* B, float* C, int M, int N, int K, int64_t lda,
-              int64_t ldb, int64_t ldc, cudaStream_t stream) {
+              int64_t ldb, int64_t ldc, cudaStream_t stream, const Tail& tail) {
   dim3 grid((N + TBN - 1) / TBN, (M + TBM - 1) / TBM);
   if (grid.y > 65535) return fail(B200_ERR_TOO_LARGE, "fp32 GEMM: too many row tiles");
   if (vec)
-    sgemm_ffma_kernel<TBM, TBN, B_NK, true><<<grid, kSgemmThreads, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc);
+    sgemm_ffma_kernel<TBM, TBN, B_NK, true><<<grid, kSgemmThreads, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc,
+                                                                                tail.bias, tail.flags);
   else
-    sgemm_ffma_kernel<TBM, TBN, B_NK, false><<<grid, kSgemmThreads, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc);
+    sgemm_ffma_kernel<TBM, TBN, B_NK, false><<<grid, kSgemmThreads, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc,
+                                                                                 tail.bias, tail.flags);
   B200_CUDA_TRY(cudaGetLastError());
   return B200_OK;
 }
 
 template <bool B_NK>
 int launch_shape(bool vec, const float* A, const float* B, float* C, int M, int N, int K, int64_t lda, int64_t ldb,
-                 int64_t ldc, cudaStream_t stream) {
+                 int64_t ldc, cudaStream_t stream, const Tail& tail) {
   // Largest tile whose grid still covers the machine (two CTAs fit on an SM): 128x128 once there
   // are at least 148 of them, else 128x64, else 64x64.
   auto tiles = [&](int tbm, int tbn) { return int64_t((M + tbm - 1) / tbm) * ((N + tbn - 1) / tbn); };
-  if (tiles(128, 128) >= 148) return launch_tb<128, 128, B_NK>(vec, A, B, C, M, N, K, lda, ldb, ldc, stream);
-  if (tiles(128, 64) >= 120) return launch_tb<128, 64, B_NK>(vec, A, B, C, M, N, K, lda, ldb, ldc, stream);
-  return launch_tb<64, 64, B_NK>(vec, A, B, C, M, N, K, lda, ldb, ldc, stream);
+  if (tiles(128, 128) >= 148) return launch_tb<128, 128, B_NK>(vec, A, B, C, M, N, K, lda, ldb, ldc, stream, tail);
+  if (tiles(128, 64) >= 120) return launch_tb<128, 64, B_NK>(vec, A, B, C, M, N, K, lda, ldb, ldc, stream, tail);
+  return launch_tb<64, 64, B_NK>(vec, A, B, C, M, N, K, lda, ldb, ldc, stream, tail);
 }
 
 }  // namespace
 
 int launch_sgemm_ffma(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
-                      int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream) {
+                      int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream, const Tail& tail) {
   if (!A || !B || !C) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
   if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
   if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30))
@@ -218,8 +240,8 @@ int launch_sgemm_ffma(const float* A, const float* B, float* C, int64_t M, int64
     return fail(B200_ERR_BAD_ARGUMENT, "a leading dimension is smaller than the row it spans");
   const bool vec = lda % 4 == 0 && ldb % 4 == 0 && reinterpret_cast<uintptr_t>(A) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(B) % 16 == 0;
-  return b_is_nk ? launch_shape<true>(vec, A, B, C, int(M), int(N), int(K), lda, ldb, ldc, stream)
-                 : launch_shape<false>(vec, A, B, C, int(M), int(N), int(K), lda, ldb, ldc, stream);
+  return b_is_nk ? launch_shape<true>(vec, A, B, C, int(M), int(N), int(K), lda, ldb, ldc, stream, tail)
+                 : launch_shape<false>(vec, A, B, C, int(M), int(N), int(K), lda, ldb, ldc, stream, tail);
 }
 
 }  // namespace b200

@@ -108,6 +108,9 @@ struct GemmArgs {
   int single_pass;  // tf32 kind only: 1 = plain fp32 operands, one pass (no split planes)
   const float* row_scale;
   const float* col_scale;
+  // Fully connected layer (floating-point outputs): out = act(sum + bias[n]), both optional.
+  const float* bias;
+  int tail_flags;  // b200_linear_flags
 };
 
 constexpr int kDefaultGroupRows = 4096;  // rows of C that share a sweep over n (keeps their A slab hot in L2)
@@ -143,9 +146,22 @@ __device__ __forceinline__ WorkItem decode_item(const GemmArgs& p, int t) {
 template <int EPI, int W = 32>
 __device__ __forceinline__ void pack_chunk(const GemmArgs& p, int n0, const uint32_t (&v)[W], float rs,
                                            uint32_t (&w)[W]) {
-  if constexpr (EPI == EPI_I32 || EPI == EPI_F32) {
+  [[maybe_unused]] const bool relu = (p.tail_flags & B200_LINEAR_RELU) != 0;
+  if constexpr (EPI == EPI_I32) {
 #pragma unroll
     for (int i = 0; i < W; ++i) w[i] = v[i];
+  } else if constexpr (EPI == EPI_F32) {
+    if (p.bias == nullptr && !relu) {
+#pragma unroll
+      for (int i = 0; i < W; ++i) w[i] = v[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < W; ++i) {
+        float x = __uint_as_float(v[i]);
+        if (p.bias != nullptr) x += __ldg(p.bias + min(n0 + i, p.N - 1));
+        w[i] = __float_as_uint(relu ? fmaxf(0.0f, x) : x);
+      }
+    }
   } else {
 #pragma unroll
     for (int i = 0; i < W / 2; ++i) {
@@ -159,6 +175,14 @@ __device__ __forceinline__ void pack_chunk(const GemmArgs& p, int n0, const uint
       } else {
         x0 = __uint_as_float(v[2 * i]);
         x1 = __uint_as_float(v[2 * i + 1]);
+        if (p.bias != nullptr) {
+          x0 += __ldg(p.bias + min(n0 + 2 * i, p.N - 1));
+          x1 += __ldg(p.bias + min(n0 + 2 * i + 1, p.N - 1));
+        }
+        if (relu) {
+          x0 = fmaxf(0.0f, x0);
+          x1 = fmaxf(0.0f, x1);
+        }
       }
       if constexpr (EPI == EPI_F16) {
         __half2 h = __floats2half2_rn(x0, x1);
@@ -825,16 +849,19 @@ int launch_kind(int kind, int epi, int bn, int cg, bool b_is_nk, const void* A, 
 int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, int64_t M, int64_t N,
                      int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
                      const float* row_scale, const float* col_scale, int force_bn,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const Tail& tail) {
   void* one[1] = {C};
   return launch_umma_gemm_multi(kind, epi, A, B, one, 1, M, N, K, lda, ldb, ldc, b_is_nk, row_scale, col_scale,
-                                force_bn, stream);
+                                force_bn, stream, tail);
 }
 
 int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void* const* C_list, int n_dest,
                            int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
-                           const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream) {
+                           const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream,
+                           const Tail& tail) {
   if (!A || !B || !C_list) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
+  if ((tail.bias || tail.flags) && (epi == EPI_I32 || epi == EPI_W8A8_BF16))
+    return fail(B200_ERR_BAD_ARGUMENT, "bias and activation exist for floating-point products only");
   if (n_dest < 1 || n_dest > kMaxDest)
     return fail(B200_ERR_BAD_ARGUMENT, "number of destinations must be between 1 and %d", kMaxDest);
   for (int g = 0; g < n_dest; ++g)
@@ -877,6 +904,8 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   args.store_mode = !c_aligned16 ? STORE_SCALAR : (g_force_store == STORE_VECTOR ? STORE_VECTOR : STORE_TMA);
   args.row_scale = row_scale;
   args.col_scale = col_scale;
+  args.bias = tail.bias;
+  args.tail_flags = tail.flags;
   args.single_pass = (kind == KIND_TF32 && g_tf32_single_pass_call) ? 1 : 0;
 
   int sms = 0;
@@ -1056,15 +1085,16 @@ size_t split_tf32_scratch_floats(int64_t M, int64_t N, int64_t K, bool b_is_nk) 
 // fp32 inputs multiplied as tf32 (the tensor cores keep sign, exponent and the top 10 mantissa bits of
 // each operand) with fp32 accumulation: one pass, no scratch.  Relative error of a product ~ 2^-10.
 int launch_sgemm_tf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                      int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream) {
+                      int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream, const Tail& tail) {
   g_tf32_single_pass_call = true;
-  int rc = launch_umma_gemm(KIND_TF32, EPI_F32, A, B, C, M, N, K, lda, ldb, ldc, b_is_nk, nullptr, nullptr, 0, stream);
+  int rc = launch_umma_gemm(KIND_TF32, EPI_F32, A, B, C, M, N, K, lda, ldb, ldc, b_is_nk, nullptr, nullptr, 0, stream,
+                            tail);
   g_tf32_single_pass_call = false;
   return rc;
 }
 
 int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
-                        int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream) {
+                        int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream, const Tail& tail) {
   if (!A || !B || !C) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
   if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
   if (lda < K || ldb < (b_is_nk ? K : N) || ldc < N)
@@ -1090,7 +1120,7 @@ int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int
   int rc = split_tf32_into(A, B, scratch, M, N, K, lda, ldb, b_is_nk, &lda_p, &ldb_p, &pb, stream);
   if (rc) return rc;
   return launch_umma_gemm(KIND_TF32, EPI_F32, scratch, pb, C, M, N, K, lda_p, ldb_p, ldc, b_is_nk, nullptr,
-                          nullptr, 0, stream);
+                          nullptr, 0, stream, tail);
 }
 
 }  // namespace b200

@@ -20,18 +20,26 @@ int fail(int code, const char* fmt, ...);
 
 enum Epilogue { EPI_I32 = 0, EPI_F32 = 1, EPI_BF16 = 2, EPI_F16 = 3, EPI_W8A8_BF16 = 4 };
 
+// Optional tail of a floating-point product (the fully connected layer): out = act(sum + bias[n]).
+// `flags` are b200_linear_flags; bias = nullptr and flags = 0 leave the product as it is.
+struct Tail {
+  const float* bias = nullptr;
+  int flags = 0;
+};
+
 // A row-major problem C[M,N] = A[M,K] * B with B either [K,N] (b_is_nk = false, N contiguous) or
 // [N,K] (b_is_nk = true, K contiguous), on the tensor cores.  `kind` is a b200::MmaKind value.
 // force_bn = 0 lets the launcher pick the tile width.
 int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, int64_t M, int64_t N,
                      int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
                      const float* row_scale, const float* col_scale, int force_bn,
-                     cudaStream_t stream);
+                     cudaStream_t stream, const Tail& tail = Tail());
 
 // Same product written to n_dest destination buffers at once (this GPU's C and peers' copies).
 int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void* const* C_list, int n_dest,
                            int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
-                           const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream);
+                           const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream,
+                           const Tail& tail = Tail());
 
 // Split-K of the single-CTA tensor-core kernels: 0 = automatic, 1 = never, n = cut K into n ranges.
 int set_split_k(int splits);
@@ -49,15 +57,17 @@ int set_tile_policy(int cg, int bn, int group_rows);
 int read_and_clear_umma_status(cudaStream_t stream, uint32_t* out);
 
 int launch_sgemm_ffma(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
-                      int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream);
+                      int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream,
+                      const Tail& tail = Tail());
 
 // 3xTF32: tensor-core fp32 GEMM from split operands (a = hi + lo, three products per term).
 int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
-                        int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream);
+                        int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream,
+                        const Tail& tail = Tail());
 
 // Single-pass tf32: fp32 operands read directly by the tensor cores (reduced precision, no scratch).
 int launch_sgemm_tf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                      int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream);
+                      int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream, const Tail& tail = Tail());
 
 int launch_naive(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                  int64_t lda, int64_t ldb, int64_t ldc, int layout, cudaStream_t stream);

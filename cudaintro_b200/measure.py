@@ -190,6 +190,37 @@ def case_f32(n, mode_name):
     return run
 
 
+def case_fc(batch, in_f, out_f, mode_name):
+    """The hidden layer of the reference's two-layer network (784 -> 512 on a batch of 20000, weights
+    [in, out], bias, ReLU) as one fused launch; `torch_ms` is the same layer as three torch calls."""
+    def run(args, device):
+        import torch
+
+        import cudaintro_b200 as cb
+
+        x = _randn((batch, in_f), torch.float32, device, 1)
+        w = _randn((in_f, out_f), torch.float32, device, 2, 0.05)
+        b = _randn((out_f,), torch.float32, device, 3, 0.1)
+        y = torch.empty((batch, out_f), dtype=torch.float32, device=device)
+        mode = getattr(cb, mode_name)
+        med, best = _time(lambda: cb.linear(x, w, b, cb.ROW_MAJOR, relu=True, bias_first=True, mode=mode, out=y),
+                          args.reps, args.warmup)
+        cb.check_device()
+        torch.backends.cuda.matmul.allow_tf32 = mode_name != "F32_FFMA"
+        tmed, _ = _time(lambda: torch.relu(torch.addmm(b, x, w)), args.reps, args.warmup)
+        torch.backends.cuda.matmul.allow_tf32 = False
+        ops = 2.0 * batch * in_f * out_f
+        sms = cb.lib.b200_sm_count()
+        if mode_name == "F32_FFMA":
+            peak, src, bound = sms * 128 * 2 * 1.965e9 / 1e12, f"{sms} SMs x 128 FP32 lanes x 2 x 1.965 GHz", "fp32 pipe"
+        else:
+            peak, src, bound = 1125.0, "nominal dense tf32", "tensor"
+        return {"bound": bound, "ms_median": med, "ms_best": best, "achieved": ops / (best * 1e-3) / 1e12,
+                "unit": "TFLOP/s", "peak": peak, "peak_source": src, "frac": ops / (best * 1e-3) / 1e12 / peak,
+                "algorithmic_bytes": 4 * (batch * in_f + in_f * out_f + out_f + batch * out_f), "torch_ms_median": tmed}
+    return run
+
+
 def case_quantize(R, C, along):
     def run(args, device):
         import cudaintro_b200 as cb
@@ -228,6 +259,8 @@ CASES = {
     "fp32_4096_3xtf32": case_f32(4096, "F32_3XTF32"),
     "fp32_1024_tf32": case_f32(1024, "F32_TF32"),
     "fp32_4096_tf32": case_f32(4096, "F32_TF32"),
+    "fc_20000x784x512_ffma": case_fc(20000, 784, 512, "F32_FFMA"),
+    "fc_20000x784x512_tf32": case_fc(20000, 784, 512, "F32_TF32"),
     "quantize_rows_8192x8192": case_quantize(8192, 8192, 0),
     "quantize_cols_8192x28672": case_quantize(8192, 28672, 1),
 }

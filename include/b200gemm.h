@@ -199,6 +199,27 @@ typedef enum b200_dtype { B200_I8 = 0, B200_F16 = 1, B200_BF16 = 2, B200_F32 = 3
 int b200_gemm_naive(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream);
 
+/* Fully connected layer, fused: Y[b][o] = act(sum_i X[b][i] * W(o,i) + bias[o]) in one launch.
+ * Replaces fullyConnectedForwardKernel followed by reluActivationKernel
+ * (MNIST/mnist_kernels.cu:87-102 and :78-84; the same pair in MNIST/mnist_cnn_kernels.cu:136-149 and
+ * the two-layer network's forwardInputToHiddenKernel / forwardHiddenToOutputKernel,
+ * MNIST/mnist_nn.cu:10-48), which run one thread per output and a second kernel for the activation.
+ *   X [batch, in_features] row-major; Y [batch, out_features] row-major, type of X;
+ *   W: B200_ROW_MAJOR_BT = [out_features, in_features] (mnist_kernels.cu, mnist_cnn_kernels.cu),
+ *      B200_ROW_MAJOR    = [in_features, out_features] (mnist_nn.cu);
+ *   bias: out_features fp32 values, or NULL;
+ *   dtype: B200_F32 (f32_mode as in b200_gemm_f32), B200_F16 or B200_BF16 (fp32 sums, bias added in
+ *      fp32 before the one rounding to 16 bits; f32_mode ignored);
+ *   flags: B200_LINEAR_RELU applies fmaxf(0, .) to the result; B200_LINEAR_BIAS_FIRST starts the
+ *      sum from the bias (mnist_nn.cu:14, mnist_cnn_kernels.cu:141) instead of adding it to the
+ *      finished sum (mnist_kernels.cu:99).  The order matters to the last bit only in
+ *      B200_F32_FFMA mode, which reproduces either reference loop exactly (fused multiply-add in
+ *      ascending i, as nvcc compiles them); the tensor-core modes add the bias to the finished sum.
+ * Alignment rules are those of the GEMM entry point the dtype and mode select. */
+typedef enum b200_linear_flags { B200_LINEAR_RELU = 1, B200_LINEAR_BIAS_FIRST = 2 } b200_linear_flags;
+int b200_linear(int dtype, const void* X, const void* W, const float* bias, void* Y, int64_t batch,
+                int64_t in_features, int64_t out_features, int w_layout, int flags, int f32_mode, void* stream);
+
 /* Same products with HOST buffers: copies A and B to the device, runs the kernels, copies C
  * back, and returns after the result is in `C`.  `dtype` selects the entry point above
  * (B200_I8 -> int32 out, B200_F16 / B200_BF16 -> 16-bit out, B200_F32 -> FFMA).  The operand

@@ -63,6 +63,8 @@ def load() -> C.CDLL:
         lib.oracle_gemm_h16.argtypes = [_p, _p, _p, _p, _i64, _i64, _i64, C.c_int, C.c_int, _p, _i64]
         lib.oracle_gemm_w8a8_bf16.argtypes = [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _i64]
         lib.oracle_quantize_absmax.argtypes = [_p, _p, _p, _i64, _i64, C.c_int]
+        lib.oracle_linear_f32.argtypes = [_p, _p, _p, _p, _i64, _i64, _i64, C.c_int, C.c_int, C.c_int]
+        lib.oracle_linear_h16.argtypes = [_p, _p, _p, _p, _p, _i64, _i64, _i64, C.c_int, C.c_int, C.c_int]
         _lib = lib
     return _lib
 
@@ -198,6 +200,40 @@ def quantize_absmax(x, along: int):
     scale = np.empty(R if along == 0 else Cc, dtype=np.float32)
     load().oracle_quantize_absmax(_ptr(q), _ptr(scale), _ptr(x), R, Cc, along)
     return q, scale
+
+
+LINEAR_RELU, LINEAR_BIAS_FIRST = 1, 2
+
+
+def linear_f32(x, w, bias, w_is_out_in=True, relu=False, bias_first=False, fused=True):
+    """Fully connected layer of the reference's MNIST networks in fp32 (see oracle_linear_f32).
+    x [batch, in]; w [out, in] when w_is_out_in else [in, out]; bias [out] or None."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    batch, in_f = x.shape
+    out_f = w.shape[0] if w_is_out_in else w.shape[1]
+    assert (w.shape[1] if w_is_out_in else w.shape[0]) == in_f
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    y = np.empty((batch, out_f), dtype=np.float32)
+    flags = (LINEAR_RELU if relu else 0) | (LINEAR_BIAS_FIRST if bias_first else 0)
+    load().oracle_linear_f32(_ptr(y), _ptr(x), _ptr(w), None if b is None else _ptr(b), batch, in_f, out_f,
+                             1 if w_is_out_in else 0, flags, 1 if fused else 0)
+    return y
+
+
+def linear_h16(x_bits, w_bits, bias, is_bf16, w_is_out_in=True, relu=False):
+    """The same layer on fp16 / bf16 bit patterns; returns (rounded 16-bit bits, fp32 before rounding)."""
+    x = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    w = np.ascontiguousarray(w_bits, dtype=np.uint16)
+    batch, in_f = x.shape
+    out_f = w.shape[0] if w_is_out_in else w.shape[1]
+    assert (w.shape[1] if w_is_out_in else w.shape[0]) == in_f
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    y16 = np.empty((batch, out_f), dtype=np.uint16)
+    y32 = np.empty((batch, out_f), dtype=np.float32)
+    load().oracle_linear_h16(_ptr(y16), _ptr(y32), _ptr(x), _ptr(w), None if b is None else _ptr(b), batch, in_f,
+                             out_f, 1 if w_is_out_in else 0, LINEAR_RELU if relu else 0, 1 if is_bf16 else 0)
+    return y16, y32
 
 
 def ref_matrix_mul_cpu(A, B, width):

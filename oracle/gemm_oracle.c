@@ -22,6 +22,13 @@
  * known-answer vectors computed from the reference formulas.  The per-row / per-column scaled
  * int8 path (W8A8) and the quantiser have no counterpart in the reference: parity unpinned for
  * those two; they are defined here.
+ *   - MNIST/mnist_kernels.cu:87-102 (fullyConnectedForwardKernel) and :78-84
+ *     (reluActivationKernel); the variants that start the sum from the bias,
+ *     MNIST/mnist_cnn_kernels.cu:136-149 and MNIST/mnist_nn.cu:10-48 (weights stored [in][out]
+ *     there).  These are device kernels in files that include OpenCV headers (not in the image),
+ *     so they can be neither compiled nor run where this oracle is built: parity unpinned for
+ *     the fully connected layer; oracle_linear_* restate the loops, with the multiply-add fused
+ *     as nvcc's default contraction makes it in device code.
  *
  * Loop order.  The product loops run i, then k, then j over a row of accumulators.  Every
  * output element still receives its products in ascending k into a single accumulator, so the
@@ -355,4 +362,63 @@ void oracle_quantize_absmax(int8_t* q, float* scale, const float* x, int64_t R, 
       if (v < -127.0f) v = -127.0f;
       q[r * C + c] = (int8_t)v;
     }
+}
+
+
+/* ------------------------------------------------------------------ fully connected layer */
+
+/* y[b][o] = act(sum_i x[b][i] * w(o,i) + bias[o]) in fp32, i ascending, one accumulator.
+ *   w_is_out_in = 1: w[o*in + i] (MNIST/mnist_kernels.cu:96); 0: w[i*out + o] (MNIST/mnist_nn.cu:17).
+ *   flags bit 0: ReLU, fmaxf(0, y) (mnist_kernels.cu:82).
+ *   flags bit 1: the sum starts from bias[o] (mnist_nn.cu:14, mnist_cnn_kernels.cu:141); otherwise
+ *                the bias is added to the finished sum (mnist_kernels.cu:99).
+ *   fused = 1: sum = fmaf(x, w, sum), what nvcc's default -fmad=true makes of `sum += x * w` in
+ *              the reference's device code; fused = 0: product and sum rounded separately. */
+void oracle_linear_f32(float* y, const float* x, const float* w, const float* bias, int64_t batch,
+                       int64_t in_f, int64_t out_f, int w_is_out_in, int flags, int fused) {
+#pragma omp parallel for schedule(static)
+  for (int64_t b = 0; b < batch; ++b) {
+    for (int64_t o = 0; o < out_f; ++o) {
+      float sum = (bias && (flags & 2)) ? bias[o] : 0.0f;
+      for (int64_t i = 0; i < in_f; ++i) {
+        const float xv = x[b * in_f + i];
+        const float wv = w_is_out_in ? w[o * in_f + i] : w[i * out_f + o];
+        if (fused) {
+          sum = fmaf(xv, wv, sum);
+        } else {
+          const float prod = xv * wv;
+          sum = sum + prod;
+        }
+      }
+      if (bias && !(flags & 2)) sum = sum + bias[o];
+      if (flags & 1) sum = fmaxf(0.0f, sum);
+      y[b * out_f + o] = sum;
+    }
+  }
+}
+
+/* The same layer on fp16 / bf16 inputs: products of two 16-bit floats are exact in fp32, the sum
+ * runs in fp32 in ascending i, the bias is added in fp32, then ReLU, then one rounding to the
+ * 16-bit type.  y32 receives the value before that rounding, y16 the rounded bits (either may be
+ * NULL). */
+void oracle_linear_h16(uint16_t* y16, float* y32, const uint16_t* x, const uint16_t* w, const float* bias,
+                       int64_t batch, int64_t in_f, int64_t out_f, int w_is_out_in, int flags, int is_bf16) {
+#pragma omp parallel for schedule(static)
+  for (int64_t b = 0; b < batch; ++b) {
+    for (int64_t o = 0; o < out_f; ++o) {
+      float sum = 0.0f;
+      for (int64_t i = 0; i < in_f; ++i) {
+        const uint16_t xb = x[b * in_f + i];
+        const uint16_t wb = w_is_out_in ? w[o * in_f + i] : w[i * out_f + o];
+        const float xv = is_bf16 ? oracle_bf16_to_f32(xb) : oracle_f16_to_f32(xb);
+        const float wv = is_bf16 ? oracle_bf16_to_f32(wb) : oracle_f16_to_f32(wb);
+        const float prod = xv * wv;
+        sum = sum + prod;
+      }
+      if (bias) sum = sum + bias[o];
+      if (flags & 1) sum = fmaxf(0.0f, sum);
+      if (y32) y32[b * out_f + o] = sum;
+      if (y16) y16[b * out_f + o] = is_bf16 ? oracle_f32_to_bf16(sum) : oracle_f32_to_f16(sum);
+    }
+  }
 }

@@ -61,6 +61,12 @@ def test_bad_arguments_are_status_codes_not_crashes(cb):
     assert lib.b200_gemm_f32(one, one, one, 8, 8, 8, 0, 0, 0, 0, 9, None) == 1
     assert lib.b200_quantize_absmax(one, one, one, 4, 4, 2, None) == 1
     assert lib.b200_gemm_naive(11, one, one, one, 4, 4, 4, 0, 0, 0, 0, None) == 1
+    # fully connected layer: pointers, sizes, weight layout, flags and dtype are checked first
+    assert lib.b200_linear(capi.F32, None, one, None, one, 4, 4, 4, 2, 0, 0, None) == 1
+    assert lib.b200_linear(capi.F32, one, one, None, one, 4, 0, 4, 2, 0, 0, None) == 1
+    assert lib.b200_linear(capi.F32, one, one, None, one, 4, 4, 4, 1, 0, 0, None) == 1   # column-major weights
+    assert lib.b200_linear(capi.F32, one, one, None, one, 4, 4, 4, 2, 8, 0, None) == 1   # unknown flag
+    assert lib.b200_linear(capi.I8, one, one, None, one, 4, 4, 4, 2, 0, 0, None) == 1
     # alignment rule of the tensor-core entry points: K = 100 int8 elements is not a 16-byte row
     assert lib.b200_gemm_i8_i32(one, one, one, 128, 128, 100, 0, 0, 0, 0, None) == 2
     assert b"16-byte" in lib.b200_last_error()

@@ -200,3 +200,48 @@ def test_fixture_directory_is_complete():
     names = {os.path.basename(p) for p in glob.glob(os.path.join(GOLDEN, "*.npz"))}
     assert {"ref_f32_32.npz", "ref_f32_96.npz", "ref_f32_unit_64.npz", "ref_i8_128.npz",
             "ref_i8_suitefill_64.npz", "ref_bf16_96.npz", "ref_f16_96.npz"} <= names
+
+
+# ------------------------------------------------------------------ fully connected layer
+
+def test_linear_known_answers_tell_the_rounding_orders_apart(oracle):
+    """Two hand-made cases.  (1) x*w = 1 + 2^-11 + 2^-24 needs 25 bits: rounded on its own it loses
+    the last one, fused into the sum with bias -(1 + 2^-11) it leaves exactly 2^-24.  (2) bias 1 and
+    products +2^24, -2^24: starting from the bias loses it (2^24 + 1 rounds to 2^24), adding it to
+    the finished sum keeps it."""
+    x = np.array([[1 + 2.0 ** -12]], dtype=np.float32)
+    w = np.array([[1 + 2.0 ** -12]], dtype=np.float32)
+    b = np.array([-(1 + 2.0 ** -11)], dtype=np.float32)
+    assert oracle.linear_f32(x, w, b, True, False, True, fused=True)[0, 0] == np.float32(2.0 ** -24)
+    assert oracle.linear_f32(x, w, b, True, False, True, fused=False)[0, 0] == 0.0
+    x = np.array([[4096.0, 4096.0]], dtype=np.float32)
+    w = np.array([[4096.0, -4096.0]], dtype=np.float32)
+    b = np.array([1.0], dtype=np.float32)
+    for fused in (True, False):
+        assert oracle.linear_f32(x, w, b, True, False, True, fused=fused)[0, 0] == 0.0   # bias first
+        assert oracle.linear_f32(x, w, b, True, False, False, fused=fused)[0, 0] == 1.0  # bias last
+    # ReLU and the two weight layouts
+    assert oracle.linear_f32(x, -w, -b, True, True, False)[0, 0] == 0.0
+    rng = np.random.default_rng(3)
+    xs = rng.standard_normal((9, 31)).astype(np.float32)
+    ws = rng.standard_normal((13, 31)).astype(np.float32)
+    bs = rng.standard_normal(13).astype(np.float32)
+    y = oracle.linear_f32(xs, ws, bs, True, True, False)
+    assert np.array_equal(y, oracle.linear_f32(xs, np.ascontiguousarray(ws.T), bs, False, True, False))
+    want = np.maximum(xs.astype(np.float64) @ ws.T.astype(np.float64) + bs, 0)
+    assert np.abs(y - want).max() < 1e-4 and (y == 0).any()
+
+
+def test_linear_16bit_is_the_fp32_sum_rounded_once(oracle):
+    rng = np.random.default_rng(4)
+    xs = rng.standard_normal((6, 40)).astype(np.float32)
+    ws = rng.standard_normal((10, 40)).astype(np.float32)
+    bs = rng.standard_normal(10).astype(np.float32)
+    xb, wb = oracle.f32_to_bf16_bits(xs), oracle.f32_to_bf16_bits(ws)
+    y16, y32 = oracle.linear_h16(xb, wb, bs, True, True, relu=False)
+    sums = oracle.linear_f32(oracle.bf16_bits_to_f32(xb), oracle.bf16_bits_to_f32(wb), bs, True, False, False, fused=False)
+    assert np.array_equal(y32, sums)
+    assert np.array_equal(y16, oracle.f32_to_bf16_bits(sums))
+    xh, wh = xs.astype(np.float16).view(np.uint16), ws.astype(np.float16).view(np.uint16)
+    y16, y32 = oracle.linear_h16(xh, wh, None, False, True, relu=True)
+    assert (y32 >= 0).all() and np.array_equal(y16.view(np.float16), y32.astype(np.float16))
