@@ -524,7 +524,9 @@ def main():
                          else "inputs fit L2: back-to-back launches re-use it"},
         "roofline": roofline,
         "clocks": clocks.summary(),
-        "gpu_launches": args.steps,
+        # kernels of this library launched inside the timed region, all ranks together: one GEMM per
+        # rank and step, plus the completion-marker kernel when the epilogue does the gather
+        "gpu_launches": args.steps * world * (2 if fused is not None else 1),
         "frac_of_nominal_peak": value / world / NOMINAL_PEAK[kind],
     }
     if e2e is not None:
