@@ -19,7 +19,7 @@ ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libb200gemm.so")
 OBJ_DIR = os.path.join(PKG, "build")
 
-SOURCES = ["api.cu", "gemm_umma.cu", "gemm_f32.cu", "simt_misc.cu", "legacy_suite.cu"]
+SOURCES = ["api.cu", "gemm_umma.cu", "gemm_skinny.cu", "gemm_f32.cu", "simt_misc.cu", "legacy_suite.cu"]
 HEADERS = ["internal.h", "ptx_sm100.cuh", os.path.join(ROOT, "include", "b200gemm.h"),
            os.path.join(ROOT, "include", "gemm_common.h")]
 

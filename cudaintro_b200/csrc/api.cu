@@ -130,9 +130,12 @@ extern "C" int b200_set_tile_policy(int cta_group, int tile_n, int group_rows) {
 }
 
 extern "C" int b200_check_device(void* stream) {
-  uint32_t st = 0;
-  int rc = read_and_clear_umma_status(static_cast<cudaStream_t>(stream), &st);
+  uint32_t st = 0, st_skinny = 0;
+  int rc = read_and_clear_umma_status(static_cast<cudaStream_t>(stream), &st);  // synchronises the stream
   if (rc) return rc;
+  rc = read_and_clear_skinny_status(&st_skinny);
+  if (rc) return rc;
+  st |= st_skinny << 8;
   if (st) return fail(B200_ERR_DEVICE_WAIT, "a tensor-core kernel gave up a bounded wait (status 0x%x)", st);
   return B200_OK;
 }

@@ -1,0 +1,444 @@
+// Skinny tensor-core products for sm_100a: C[M,N] = A[M,K] * B with M <= 32 rows (a decode batch
+// against a wide weight matrix), fp16 / bf16 in and out, fp32 accumulation.
+//
+// Such a product streams B from HBM once and does almost no arithmetic, so what counts is that every
+// SM streams an equal share of B.  One SM cannot keep more than about 64 KB of TMA loads in flight,
+// which from DRAM is 50-60 GB/s: a [4096 -> 11008] layer cut into 86 column tiles of 128 therefore
+// runs at the speed of 86 SMs however deep the ring is.  Here a tile of BN columns (128, 192 or 256)
+// is shared by a thread-block cluster of S CTAs that each stream one K range of it; tiles x S is
+// chosen close to the SM count.  The partial sums meet on chip:
+//
+//   1. every CTA runs the usual ring (TMA producer -> tcgen05.mma into tensor memory) over its K range;
+//   2. warp 0 of every CTA copies its 32 accumulator rows out of tensor memory into the slot of its
+//      K range in an exchange area in the leader's shared memory (the leader with plain stores, the
+//      others through distributed shared memory), 16 bytes per lane and store;
+//   3. cluster barrier: the slots are complete and visible to the leader;
+//   4. all four warps of the leader add the slots in K order (so the result does not depend on
+//      timing), apply the optional bias / ReLU tail, round once to the 16-bit type and store the rows
+//      below M.  Splitting 2 from 4 matters: one warp alone needs about 0.5 us per 32 columns for the
+//      arithmetic of step 4, and only a warp whose index is a multiple of four may read lanes 0-31 of
+//      tensor memory.
+//
+// Only 32 rows of A are staged per k-block.  The MMA is still 128 rows tall and reads its other 96
+// operand rows from the bytes that follow in the stage (the B tile); an accumulator row depends on its
+// own row of A only, so rows 32..127 hold garbage that is never read back.  (Staging the 32 rows four
+// times, so that every warp finds them in its own quarter of tensor memory, was measured: the extra
+// 12 KB of TMA traffic per stage slowed the stream of B by more than the parallel read-out saved.)
+//
+// CTA = four warps.  Lane 0 of warp 0 issues the TMA loads, lane 0 of warp 1 the MMAs (warp 1 owns
+// the TMEM allocation); warp 0 then does step 2 and all warps step 4.  Every mbarrier wait is bounded;
+// the barriers are reached by every thread on every path, including the one where a wait was given up.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstring>
+#include <mutex>
+
+#include "internal.h"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+namespace {
+
+__device__ uint32_t g_skinny_status = 0;  // bit 0: a bounded wait ran out somewhere
+
+constexpr int kSkThreads = 128;
+constexpr int kSkRows = 32;              // rows of A staged, rows of C produced
+constexpr int kSkBK = 64;                // 16-bit elements of K per stage (one 128-byte swizzle row)
+constexpr int kSkABytes = kSkRows * 128;
+constexpr int kSkMaxStages = 8;
+constexpr int kSkSmemBudget = 227 * 1024;
+constexpr int kSkTailBytes = 256;        // barriers, TMEM slot, abort flag
+
+struct SkinnyArgs {
+  void* C;
+  int64_t ldc;
+  int M, N, K;
+  int bn;            // tile width: 128, 192 or 256
+  int splits;        // CTAs per cluster = K ranges per tile
+  int kb_per_split;  // k-blocks per range (the last range may be shorter, never empty)
+  int stages;
+  int kind;          // KIND_F16 or KIND_BF16
+  int b_is_nk;       // B is [N,K] (K contiguous) instead of [K,N]
+  int vec_store;     // rows of C are 16-byte aligned
+  const float* bias;
+  int tail_flags;    // b200_linear_flags
+};
+
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kSkThreads, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const SkinnyArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int b_bytes = p.bn * 128;
+  const int stage_bytes = kSkABytes + b_bytes;
+  // ring of stages | exchange area (the leader's is written by the other CTAs of the cluster) | barriers
+  float* exch = reinterpret_cast<float*>(smem + p.stages * stage_bytes);  // [S][bn / 4][32 rows][4] floats
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes + p.splits * p.bn * 128);
+  uint64_t* full_bar = bars;                    // [stages] producer -> MMA
+  uint64_t* empty_bar = bars + kSkMaxStages;    // [stages] MMA -> producer
+  uint64_t* acc_full = bars + 2 * kSkMaxStages; // MMA -> epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int S = p.splits;
+  const uint32_t rank = S > 1 ? cluster_cta_rank() : 0u;  // 0 = the CTA that finishes the tile
+  const int tile = int(blockIdx.x) / S;
+  const int n0 = tile * p.bn;
+  const int num_kb = (p.K + kSkBK - 1) / kSkBK;
+  const int kb0 = int(rank) * p.kb_per_split;
+  const int kb_count = min(p.kb_per_split, num_kb - kb0);  // >= 1 by construction of the launch
+  const uint32_t tmem_cols = p.bn <= 128 ? 128u : 256u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  // In a cluster this is also the point after which every CTA of it is known to be running, which
+  // writing into another CTA's shared memory requires; it costs nothing at the tail that way.
+  __syncwarp();
+  if (p.splits > 1) cluster_sync_all(); else __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Nothing above touched global memory.  Wait for the kernel this launch was serialised behind (a
+  // no-op without a programmatic dependency) and let the next kernel begin its own set-up.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < kb_count; ++i) {
+        if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) break;
+        uint8_t* sa = smem + stage * stage_bytes;
+        uint8_t* sb = sa + kSkABytes;
+        const int k = (kb0 + i) * kSkBK;
+        mbar_arrive_expect_tx(&full_bar[stage], uint32_t(stage_bytes));
+        tma_load_2d(sa, &tmap_a, &full_bar[stage], k, 0);
+        if (p.b_is_nk) {
+          tma_load_2d(sb, &tmap_b, &full_bar[stage], k, n0);
+        } else {
+          for (int s = 0; s < p.bn / 64; ++s)
+            tma_load_2d(sb + s * (kSkBK * 128), &tmap_b, &full_bar[stage], n0 + s * 64, k);
+        }
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_instr_desc(p.kind, 128, p.bn, 0, p.b_is_nk ? 0 : 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = 0; i < kb_count; ++i) {
+        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+        const uint32_t sb = sa + kSkABytes;
+        const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
+        const uint64_t b_desc = p.b_is_nk ? make_smem_desc_sw128(sb, 16, 1024)
+                                          : make_smem_desc_sw128(sb, kSkBK * 128, 1024);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // 16 elements of K per instruction
+          const uint64_t a_adv = uint64_t((j * 32) >> 4);
+          const uint64_t b_adv = p.b_is_nk ? uint64_t((j * 32) >> 4) : uint64_t((j * 16 * 128) >> 4);
+          umma<KIND_F16>(tmem_base, a_desc + a_adv, b_desc + b_adv, idesc, (i | j) != 0 ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[stage]);
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) umma_commit(acc_full);
+    }
+    __syncwarp();
+  }
+  const int chunks = min(p.bn / 32, (p.N - n0 + 31) / 32);  // 32-column chunks with a column inside C
+  if (warp == 0) {
+    // ---------------------------------------------------------------- step 2: tensor memory -> slot `rank`
+    bool acc_ready = mbar_wait_bounded(acc_full, 0u, abort_flag);
+    acc_ready = __all_sync(0xffffffffu, acc_ready) != 0;  // the warp acts as one from here on
+    tc_fence_after_sync();
+    if (acc_ready) {
+      // [range][column / 4][row][4]: a lane owns a row and writes 4 columns per store
+      const uint32_t slot = map_to_cta(smem_u32(exch), 0) + uint32_t(int(rank) * p.bn * 128 + lane * 16);
+      for (int c0 = 0; c0 < chunks; c0 += 4) {  // up to four chunks fetched before the one wait
+        uint32_t v[4][32];
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          if (c0 + g < chunks) tmem_ld_32x32(tmem_base + uint32_t((c0 + g) * 32), v[g]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (c0 + g < chunks) {
+            const uint32_t dst = slot + uint32_t((c0 + g) * 8 * 512);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              st_cluster_v4(dst + uint32_t(q * 512), v[g][4 * q], v[g][4 * q + 1], v[g][4 * q + 2], v[g][4 * q + 3]);
+          }
+        }
+      }
+    }
+  }
+  // Step 3: every slot is complete and visible to the leader.
+  __syncwarp();
+  if (S > 1) cluster_sync_all(); else __syncthreads();
+
+  if (rank == 0 && *abort_flag == 0u) {
+    // ---------------------------------------------------------------- step 4: add, finish, store
+    // A thread owns row `lane` and takes groups of 8 columns (two 16-byte units of a slot): warp w
+    // the groups w, w + 4, ...  Reads of a slot are conflict-free (consecutive lanes, 16 bytes each).
+    const bool relu = (p.tail_flags & B200_LINEAR_RELU) != 0;
+    const int row = lane;
+    const float4* slots = reinterpret_cast<const float4*>(exch) + lane;
+    for (int g = warp; g < chunks * 4; g += 4) {
+      const int nc = n0 + g * 8;
+      if (nc >= p.N) break;
+      float x[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = 0.0f;
+      for (int r = 0; r < S; ++r) {
+        const float4* part = slots + (r * (p.bn / 4) + g * 2) * 32;
+        const float4 t0 = part[0], t1 = part[32];
+        if (r == 0) {
+          x[0] = t0.x; x[1] = t0.y; x[2] = t0.z; x[3] = t0.w;
+          x[4] = t1.x; x[5] = t1.y; x[6] = t1.z; x[7] = t1.w;
+        } else {
+          x[0] += t0.x; x[1] += t0.y; x[2] += t0.z; x[3] += t0.w;
+          x[4] += t1.x; x[5] += t1.y; x[6] += t1.z; x[7] += t1.w;
+        }
+      }
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float x0 = x[2 * j], x1 = x[2 * j + 1];
+        if (p.bias != nullptr) {
+          x0 += __ldg(p.bias + min(nc + 2 * j, p.N - 1));
+          x1 += __ldg(p.bias + min(nc + 2 * j + 1, p.N - 1));
+        }
+        if (relu) {
+          x0 = fmaxf(0.0f, x0);
+          x1 = fmaxf(0.0f, x1);
+        }
+        if (p.kind == KIND_F16) {
+          __half2 h = __floats2half2_rn(x0, x1);
+          w[j] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+          __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+          w[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+      }
+      if (row < p.M) {
+        uint16_t* dst = static_cast<uint16_t*>(p.C) + int64_t(row) * p.ldc + nc;
+        if (p.vec_store && nc + 8 <= p.N) {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (nc + j < p.N) dst[j] = uint16_t(w[j >> 1] >> ((j & 1) * 16));
+        }
+      }
+    }
+  }
+
+  // Every role gets here: its loop ended or its wait was given up.
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicOr(&g_skinny_status, 1u);
+    // Give copies and MMAs still in flight time to land before shared and tensor memory go away.
+    uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// Clusters of `splits` CTAs the device can hold at once.  Every configuration takes more than half
+// of an SM's shared memory, so one CTA per SM it is; the query is made with the largest footprint.
+int max_resident_clusters(int splits, int* out) {
+  static std::mutex mu;
+  static int cache[64][9];  // [device][splits]: 0 = unknown
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 64 && cache[dev][splits]) { *out = cache[dev][splits] > 0 ? cache[dev][splits] : 0; return B200_OK; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(splits));
+  cfg.blockDim = dim3(kSkThreads);
+  cfg.dynamicSmemBytes = size_t(kSkSmemBudget);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = unsigned(splits);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  B200_CUDA_TRY(cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemBudget));
+  B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, gemm_skinny_kernel, &cfg));
+  if (dev < 64) cache[dev][splits] = n > 0 ? n : -1;
+  *out = n;
+  return B200_OK;
+}
+
+}  // namespace
+
+int read_and_clear_skinny_status(uint32_t* out) {
+  uint32_t zero = 0;
+  B200_CUDA_TRY(cudaMemcpyFromSymbol(out, g_skinny_status, sizeof(uint32_t)));
+  if (*out) B200_CUDA_TRY(cudaMemcpyToSymbol(g_skinny_status, &zero, sizeof(uint32_t)));
+  return B200_OK;
+}
+
+// Decides whether the product is one this kernel should take and, if so, launches it.
+//   *used = false and B200_OK: not taken (the caller runs the general kernel).
+//   force = true: the caller insists (tile policy 3); a product that does not qualify is an error.
+int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                       int64_t ldb, int64_t ldc, bool b_is_nk, const Tail& tail, int force_bn, bool force,
+                       int64_t general_cost, cudaStream_t stream, bool* used) {
+  *used = false;
+  if ((kind != KIND_F16 && kind != KIND_BF16) || M > kSkRows) {
+    if (force) return fail(B200_ERR_UNSUPPORTED, "the skinny kernel takes fp16 / bf16 products of at most %d rows", kSkRows);
+    return B200_OK;
+  }
+  int sms = 0;
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  B200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int num_kb = int((K + kSkBK - 1) / kSkBK);
+
+  // Tile width and cluster size: the smallest share of B per CTA (columns x k-blocks) among the
+  // configurations that run in one wave, with a small charge per extra range for the exchange.
+  int best_bn = 0, best_s = 0, best_per = 0, best_stages = 0;
+  int64_t best_cost = 0;
+  for (int bn = 128; bn <= 256; bn += 64) {
+    if (force_bn && bn != force_bn) continue;
+    const int stage_bytes = kSkABytes + bn * 128;
+    const int64_t tiles = (N + bn - 1) / bn;
+    if (tiles > sms) continue;
+    int s_max = int(sms / tiles);
+    if (s_max > 8) s_max = 8;
+    if (s_max > num_kb) s_max = num_kb;
+    // Cluster sizes 1, 2, 4, 8 only: clusters of 3 did not all become resident together on a B200
+    // (whatever the occupancy query said) and the product then took a second wave.
+    for (int s_try = s_max >= 8 ? 8 : (s_max >= 4 ? 4 : (s_max >= 2 ? 2 : 1)); s_try >= 1; s_try >>= 1) {
+      const int per = (num_kb + s_try - 1) / s_try;
+      const int s = (num_kb + per - 1) / per;  // no empty range
+      if (s & (s - 1)) continue;
+      // shared memory: ring, then s slots of 32 rows x bn fp32 in the exchange area; at least three stages
+      int stages = (kSkSmemBudget - 1024 - kSkTailBytes - s * bn * 128) / stage_bytes;
+      if (stages > kSkMaxStages) stages = kSkMaxStages;
+      if (stages < 3) continue;
+      if (s > 1) {
+        int resident = 0;
+        int rc = max_resident_clusters(s, &resident);
+        if (rc) return rc;
+        if (resident < tiles) continue;  // a second wave of clusters would cost more than it saves
+      }
+      const int64_t cost = int64_t(bn) * per + (s > 1 ? 384 : 0);  // the exchange is worth about 1 us of streaming
+      if (best_bn == 0 || cost < best_cost) {
+        best_bn = bn; best_s = s; best_per = per; best_stages = stages; best_cost = cost;
+      }
+      break;  // smaller clusters of this width only stream more per CTA
+    }
+  }
+  if (best_bn == 0) {
+    if (force) return fail(B200_ERR_UNSUPPORTED, "no one-wave configuration of the skinny kernel fits N = %lld", (long long)N);
+    return B200_OK;
+  }
+  // Not worth a different kernel unless every SM streams clearly less than it would in the general one.
+  if (!force && best_cost * 10 > general_cost * 9) return B200_OK;
+
+  if ((lda * 2) % 16 || (ldb * 2) % 16 || reinterpret_cast<uintptr_t>(A) % 16 || reinterpret_cast<uintptr_t>(B) % 16) {
+    if (force) return fail(B200_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned A and B pointers and leading dimensions");
+    return B200_OK;  // the general path reports it
+  }
+  if (reinterpret_cast<uintptr_t>(C) % 2) return fail(B200_ERR_UNSUPPORTED, "C is not aligned to its element size");
+
+  const int smem_bytes = best_stages * (kSkABytes + best_bn * 128) + best_s * best_bn * 128 + 1024 + kSkTailBytes;
+  static thread_local int attr_dev = -1;
+  if (dev != attr_dev) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemBudget));
+    attr_dev = dev;
+  }
+  CUtensorMap ma, mb;
+  int rc = encode_operand_map(&ma, kind, A, M, K, lda, kSkBK, kSkRows, false);
+  if (rc) return rc;
+  rc = b_is_nk ? encode_operand_map(&mb, kind, B, N, K, ldb, kSkBK, best_bn, false)
+               : encode_operand_map(&mb, kind, B, K, N, ldb, 64, kSkBK, false);
+  if (rc) return rc;
+
+  SkinnyArgs args;
+  memset(&args, 0, sizeof(args));
+  args.C = C;
+  args.ldc = ldc;
+  args.M = int(M);
+  args.N = int(N);
+  args.K = int(K);
+  args.bn = best_bn;
+  args.splits = best_s;
+  args.kb_per_split = best_per;
+  args.stages = best_stages;
+  args.kind = kind;
+  args.b_is_nk = b_is_nk ? 1 : 0;
+  args.vec_store = ((ldc * 2) % 16 == 0 && reinterpret_cast<uintptr_t>(C) % 16 == 0) ? 1 : 0;
+  args.bias = tail.bias;
+  args.tail_flags = tail.flags;
+
+  const int tiles = int((N + best_bn - 1) / best_bn);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(tiles * best_s));
+  cfg.blockDim = dim3(kSkThreads);
+  cfg.dynamicSmemBytes = size_t(smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int nattr = 0;
+  if (dependent_launch_enabled()) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  if (best_s > 1) {
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = unsigned(best_s);
+    attr[nattr].val.clusterDim.y = 1;
+    attr[nattr].val.clusterDim.z = 1;
+    ++nattr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = unsigned(nattr);
+  B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_skinny_kernel, ma, mb, args));
+  *used = true;
+  return B200_OK;
+}
+
+}  // namespace b200

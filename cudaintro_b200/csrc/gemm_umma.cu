@@ -805,9 +805,24 @@ int launch_bn(int bn, int cg, bool b_nk, const void* A, const void* B, GemmArgs 
 
 }  // namespace
 
+int encode_operand_map(CUtensorMap* map, int kind, const void* base, int64_t rows, int64_t cols, int64_t ld,
+                       int box_cols, int box_rows, bool chunks32) {
+  return make_map(map, kind, base, rows, cols, ld, box_cols, box_rows, chunks32);
+}
+
+bool dependent_launch_enabled() { return g_use_pdl; }
+
 int set_tile_policy(int cg, int bn, int group_rows) {
   if (group_rows < 0 || (group_rows % 256) != 0)
     return fail(B200_ERR_BAD_ARGUMENT, "tile policy: group rows must be a non-negative multiple of 256");
+  if (cg == 3) {  // the K-split cluster kernel for skinny products, at a width of its own choice or a given one
+    if (bn != 0 && bn != 128 && bn != 192 && bn != 256)
+      return fail(B200_ERR_BAD_ARGUMENT, "tile policy: the skinny kernel has widths 128, 192 and 256");
+    g_force_cg = cg;
+    g_force_bn = bn;
+    g_group_rows = group_rows;
+    return B200_OK;
+  }
   if ((cg != 0 && cg != 1 && cg != 2) || (bn != 0 && bn != 64 && bn != 128 && bn != 256))
     return fail(B200_ERR_BAD_ARGUMENT, "tile policy: cta group must be 0, 1 or 2 and width 0, 64, 128 or 256");
   if (cg == 2 && bn != 0 && bn != 256) return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs need 256-wide tiles");
@@ -911,12 +926,16 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   int sms = 0;
   int rc = sm_count_of_current_device(&sms);
   if (rc) return rc;
-  int bn = force_bn ? force_bn : g_force_bn;
-  int cg = g_force_cg;
+  const bool skinny_forced = g_force_cg == 3;  // tile policy 3: the K-split cluster kernel or nothing
+  const bool half_kind = kind == KIND_F16 || kind == KIND_BF16;
+  if (skinny_forced && !(half_kind && n_dest == 1))
+    return fail(B200_ERR_UNSUPPORTED, "the skinny kernel takes fp16 / bf16 products with one destination");
+  int bn = force_bn ? force_bn : (skinny_forced ? 0 : g_force_bn);
+  int cg = skinny_forced ? 1 : g_force_cg;
   if (cg == 0) {
     // CTA pairs (256 x 256 tiles) once they give every pair of SMs a tile; single CTAs below that.
     const int64_t pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-    cg = (bn == 0 || bn == 256) && pair_tiles >= sms / 2 ? 2 : 1;
+    cg = (bn == 0 || bn == 256) && M > BM && pair_tiles >= sms / 2 ? 2 : 1;  // a pair needs more than one CTA's rows
   }
   if (cg == 2) bn = 256;
   if (bn == 0) {
@@ -931,6 +950,20 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
     }
   }
   if (kind == KIND_I8 && !b_is_nk && bn < 128) bn = 128;  // an int8 span of N is 128 elements wide
+
+  // A 16-bit product of at most 32 rows streams B and little else.  If splitting K inside clusters
+  // lets every SM stream clearly less than the tiles chosen above would, that kernel takes it.
+  const bool nothing_forced = force_bn == 0 && g_force_bn == 0 && g_force_cg == 0 && g_force_splits == 0 &&
+                              g_force_store == 0;
+  if (half_kind && n_dest == 1 && (skinny_forced || (nothing_forced && M <= 32))) {
+    const int64_t k_blocks = (K + 63) / 64;
+    const int64_t tiles = int64_t(args.tiles_m) * ((N + bn - 1) / bn);
+    const int64_t general_cost = ((tiles + sms - 1) / sms) * bn * k_blocks;
+    bool used = false;
+    rc = launch_skinny_gemm(kind, A, B, C_list[0], M, N, K, lda, ldb, ldc, b_is_nk, tail, skinny_forced ? g_force_bn : 0,
+                            skinny_forced, general_cost, stream, &used);
+    if (rc || used) return rc;
+  }
 
   // Work items: whole tiles, then (on request only, b200_set_split_k(n >= 2)) tiles cut along K:
   //  * a product with more tiles than SMs (or SM pairs) whose last wave is less than half full gets

@@ -1,6 +1,7 @@
 // Declarations shared by the translation units of libb200gemm (not part of the public ABI).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -40,6 +41,24 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
                            int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk,
                            const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream,
                            const Tail& tail = Tail());
+
+// The same kind of product for at most 32 rows of 16-bit A: tiles shared by clusters that split K and
+// add their partial sums through distributed shared memory (gemm_skinny.cu).  *used tells whether the
+// kernel took the product; `general_cost` is what one SM would stream in the general kernel
+// (tile columns x k-blocks x waves), the yardstick it has to beat unless `force` is set.
+int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                       int64_t ldb, int64_t ldc, bool b_is_nk, const Tail& tail, int force_bn, bool force,
+                       int64_t general_cost, cudaStream_t stream, bool* used);
+int read_and_clear_skinny_status(uint32_t* out);
+
+// 2-D tensor map over a row-major [rows, cols] matrix of MmaKind `kind` elements with leading
+// dimension `ld`: box = box_cols x box_rows, 128-byte swizzle (on 32-byte chunks if `chunks32`),
+// zero fill outside the matrix.
+int encode_operand_map(CUtensorMap* map, int kind, const void* base, int64_t rows, int64_t cols, int64_t ld,
+                       int box_cols, int box_rows, bool chunks32);
+
+// Whether kernels are launched with programmatic stream serialisation (set_dependent_launch).
+bool dependent_launch_enabled();
 
 // Split-K of the single-CTA tensor-core kernels: 0 = automatic, 1 = never, n = cut K into n ranges.
 int set_split_k(int splits);

@@ -288,6 +288,8 @@ def main():
     ap.add_argument("--list", action="store_true")
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--policy", default="", help="tile policy for every case: cta_group,tile_n (e.g. 1,128 forces the "
+                    "general kernel with 128-wide tiles, 3,0 the skinny K-split kernel); default: automatic")
     args = ap.parse_args()
     if args.list:
         print("\n".join(CASES))
@@ -296,8 +298,16 @@ def main():
     for n in names:
         if n not in CASES:
             raise SystemExit(f"unknown case {n!r}; try --list")
+    if args.policy:
+        import cudaintro_b200 as cb
+
+        cg, bn = (int(v) for v in args.policy.split(","))
+        cb.set_tile_policy(cg, bn, 0)
     for name in names:
-        print(json.dumps(run_cases([name], args.reps, args.warmup)[name]), flush=True)
+        res = run_cases([name], args.reps, args.warmup)[name]
+        if args.policy:
+            res["tile_policy"] = args.policy
+        print(json.dumps(res), flush=True)
     return 0
 
 

@@ -67,7 +67,10 @@ int b200_sm_count(void);
  * forces the tensor-core kernels to use single CTAs (cta_group = 1) or CTA pairs (2) per tile
  * and a tile width of 64, 128 or 256 columns; `group_rows` (a multiple of 256) is how many rows
  * of C share one sweep across N in the tile order.  0 restores the automatic choice of each.
- * CTA pairs exist for 256-wide tiles only.  Integer results do not depend on the policy;
+ * CTA pairs exist for 256-wide tiles only.  cta_group = 3 sends fp16 / bf16 products of at most
+ * 32 rows to the K-split cluster kernel (tile_n 0, 128, 192 or 256) and makes every other product
+ * fail with B200_ERR_UNSUPPORTED; without a policy that kernel is chosen by itself when it lets
+ * every SM stream clearly less of B.  Integer results do not depend on the policy;
  * floating-point results may differ in the last bits (the order of the K blocks changes). */
 int b200_set_tile_policy(int cta_group, int tile_n, int group_rows);
 
