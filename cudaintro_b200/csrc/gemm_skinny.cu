@@ -1,33 +1,34 @@
-// Skinny tensor-core products for sm_100a: C[M,N] = A[M,K] * B with M <= 32 rows (a decode batch
-// against a wide weight matrix), fp16 / bf16 in and out, fp32 accumulation.
+// Skinny tensor-core products for sm_100a: C[M,N] = A[M,K] * B with M <= 128 rows (a decode or
+// small-prefill batch against a wide weight matrix), fp16 / bf16 in and out, fp32 accumulation.
 //
-// Such a product streams B from HBM once and does almost no arithmetic, so what counts is that every
+// Such a product streams B from HBM once and does little arithmetic, so what counts is that every
 // SM streams an equal share of B.  One SM cannot keep more than about 64 KB of TMA loads in flight,
 // which from DRAM is 50-60 GB/s: a [4096 -> 11008] layer cut into 86 column tiles of 128 therefore
 // runs at the speed of 86 SMs however deep the ring is.  Here a tile of BN columns (128, 192 or 256)
-// is shared by a thread-block cluster of S CTAs that each stream one K range of it; tiles x S is
-// chosen close to the SM count.  The partial sums meet on chip:
+// is shared by a thread-block cluster of S CTAs (1, 2, 4 or 8) that each stream one K range of it;
+// tiles x S is chosen close to the SM count.  The partial sums meet on chip, reduce-scatter fashion:
 //
 //   1. every CTA runs the usual ring (TMA producer -> tcgen05.mma into tensor memory) over its K range;
-//   2. warp 0 of every CTA copies its 32 accumulator rows out of tensor memory into the slot of its
-//      K range in an exchange area in the leader's shared memory (the leader with plain stores, the
-//      others through distributed shared memory), 16 bytes per lane and store;
-//   3. cluster barrier: the slots are complete and visible to the leader;
-//   4. all four warps of the leader add the slots in K order (so the result does not depend on
-//      timing), apply the optional bias / ReLU tail, round once to the 16-bit type and store the rows
-//      below M.  Splitting 2 from 4 matters: one warp alone needs about 0.5 us per 32 columns for the
-//      arithmetic of step 4, and only a warp whose index is a multiple of four may read lanes 0-31 of
-//      tensor memory.
+//   2. the columns of the tile are dealt out to the CTAs of the cluster, BN / S each.  Every CTA moves
+//      its accumulator out of tensor memory, each 32-column chunk into the exchange area of the CTA that
+//      owns those columns (its own included; the others' through distributed shared memory), 16 bytes
+//      per lane and store, into the slot of its K range;
+//   3. cluster barrier: the slots are complete and visible to their owners;
+//   4. every CTA adds the slots of its columns in K order (so the result does not depend on timing),
+//      applies the optional bias / ReLU tail, rounds once to the 16-bit type and stores the rows
+//      below M.  All four warps share this work whatever M is; only step 2 is tied to the warp that
+//      may read a given quarter of tensor memory (a single warp needs about 0.5 us per 32 columns
+//      for the arithmetic of step 4, which is why the two steps are separate).
 //
-// Only 32 rows of A are staged per k-block.  The MMA is still 128 rows tall and reads its other 96
-// operand rows from the bytes that follow in the stage (the B tile); an accumulator row depends on its
-// own row of A only, so rows 32..127 hold garbage that is never read back.  (Staging the 32 rows four
-// times, so that every warp finds them in its own quarter of tensor memory, was measured: the extra
-// 12 KB of TMA traffic per stage slowed the stream of B by more than the parallel read-out saved.)
+// Only R = 32, 64, 96 or 128 rows of A are staged per k-block (M rounded up to 32).  The MMA is
+// always 128 rows tall and reads its other operand rows from the bytes that follow in the stage (the
+// B tile); an accumulator row depends on its own row of A only, so rows R..127 hold garbage that
+// is never read back.
 //
 // CTA = four warps.  Lane 0 of warp 0 issues the TMA loads, lane 0 of warp 1 the MMAs (warp 1 owns
-// the TMEM allocation); warp 0 then does step 2 and all warps step 4.  Every mbarrier wait is bounded;
-// the barriers are reached by every thread on every path, including the one where a wait was given up.
+// the TMEM allocation); warp q < R / 32 then does step 2 for rows 32q..32q+31 and all warps step 4.
+// Every mbarrier wait is bounded; the barriers are reached by every thread on every path, including
+// the one where a wait was given up.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -45,9 +46,8 @@ namespace {
 __device__ uint32_t g_skinny_status = 0;  // bit 0: a bounded wait ran out somewhere
 
 constexpr int kSkThreads = 128;
-constexpr int kSkRows = 32;              // rows of A staged, rows of C produced
+constexpr int kSkMaxRows = 128;          // rows of C one launch can produce
 constexpr int kSkBK = 64;                // 16-bit elements of K per stage (one 128-byte swizzle row)
-constexpr int kSkABytes = kSkRows * 128;
 constexpr int kSkMaxStages = 8;
 constexpr int kSkSmemBudget = 227 * 1024;
 constexpr int kSkTailBytes = 256;        // barriers, TMEM slot, abort flag
@@ -56,8 +56,9 @@ struct SkinnyArgs {
   void* C;
   int64_t ldc;
   int M, N, K;
+  int rows;          // R: rows of A staged = M rounded up to a multiple of 32
   int bn;            // tile width: 128, 192 or 256
-  int splits;        // CTAs per cluster = K ranges per tile
+  int splits;        // S: CTAs per cluster = K ranges per tile; divides bn / 32
   int kb_per_split;  // k-blocks per range (the last range may be shorter, never empty)
   int stages;
   int kind;          // KIND_F16 or KIND_BF16
@@ -77,21 +78,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                    const SkinnyArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int b_bytes = p.bn * 128;
-  const int stage_bytes = kSkABytes + b_bytes;
-  // ring of stages | exchange area (the leader's is written by the other CTAs of the cluster) | barriers
-  float* exch = reinterpret_cast<float*>(smem + p.stages * stage_bytes);  // [S][bn / 4][32 rows][4] floats
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes + p.splits * p.bn * 128);
+  const int R = p.rows;
+  const int S = p.splits;
+  const int a_bytes = R * 128;
+  const int stage_bytes = a_bytes + p.bn * 128;
+  // ring of stages | exchange area (written by every CTA of the cluster) | barriers
+  // Exchange area: [K range][16-byte unit of this CTA's columns][row][4 floats]; S * (bn / S) * R * 4 bytes.
+  float* exch = reinterpret_cast<float*>(smem + p.stages * stage_bytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes + p.bn * R * 4);
   uint64_t* full_bar = bars;                    // [stages] producer -> MMA
   uint64_t* empty_bar = bars + kSkMaxStages;    // [stages] MMA -> producer
-  uint64_t* acc_full = bars + 2 * kSkMaxStages; // MMA -> epilogue
+  uint64_t* acc_full = bars + 2 * kSkMaxStages; // MMA -> the warps that read tensor memory
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int S = p.splits;
-  const uint32_t rank = S > 1 ? cluster_cta_rank() : 0u;  // 0 = the CTA that finishes the tile
+  const uint32_t rank = S > 1 ? cluster_cta_rank() : 0u;
   const int tile = int(blockIdx.x) / S;
   const int n0 = tile * p.bn;
   const int num_kb = (p.K + kSkBK - 1) / kSkBK;
@@ -118,7 +121,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   // In a cluster this is also the point after which every CTA of it is known to be running, which
   // writing into another CTA's shared memory requires; it costs nothing at the tail that way.
   __syncwarp();
-  if (p.splits > 1) cluster_sync_all(); else __syncthreads();
+  if (S > 1) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -135,7 +138,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       for (int i = 0; i < kb_count; ++i) {
         if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) break;
         uint8_t* sa = smem + stage * stage_bytes;
-        uint8_t* sb = sa + kSkABytes;
+        uint8_t* sb = sa + a_bytes;
         const int k = (kb0 + i) * kSkBK;
         mbar_arrive_expect_tx(&full_bar[stage], uint32_t(stage_bytes));
         tma_load_2d(sa, &tmap_a, &full_bar[stage], k, 0);
@@ -160,7 +163,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t sa = smem_u32(smem + stage * stage_bytes);
-        const uint32_t sb = sa + kSkABytes;
+        const uint32_t sb = sa + uint32_t(a_bytes);
         const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
         const uint64_t b_desc = p.b_is_nk ? make_smem_desc_sw128(sb, 16, 1024)
                                           : make_smem_desc_sw128(sb, kSkBK * 128, 1024);
@@ -177,53 +180,62 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
     __syncwarp();
   }
+
   const int chunks = min(p.bn / 32, (p.N - n0 + 31) / 32);  // 32-column chunks with a column inside C
-  if (warp == 0) {
-    // ---------------------------------------------------------------- step 2: tensor memory -> slot `rank`
+  const int own_chunks = p.bn / 32 / S;                     // chunks whose columns one CTA finishes
+  const int own_units = own_chunks * 8;                     // 16-byte units (4 columns) of those
+  if (warp < R / 32) {
+    // ---------------------------------------------------------------- step 2: tensor memory -> slots
     bool acc_ready = mbar_wait_bounded(acc_full, 0u, abort_flag);
     acc_ready = __all_sync(0xffffffffu, acc_ready) != 0;  // the warp acts as one from here on
     tc_fence_after_sync();
     if (acc_ready) {
-      // [range][column / 4][row][4]: a lane owns a row and writes 4 columns per store
-      const uint32_t slot = map_to_cta(smem_u32(exch), 0) + uint32_t(int(rank) * p.bn * 128 + lane * 16);
+      const uint32_t quarter = tmem_base + (uint32_t(warp * 32) << 16);  // rows 32 * warp + lane
+      // byte offset of (slot of this K range, unit 0, this thread's row) inside an exchange area
+      const uint32_t mine = uint32_t(((int(rank) * own_units) * R + warp * 32 + lane) * 16);
+      const uint32_t exch_addr = smem_u32(exch);
       for (int c0 = 0; c0 < chunks; c0 += 4) {  // up to four chunks fetched before the one wait
         uint32_t v[4][32];
 #pragma unroll
         for (int g = 0; g < 4; ++g)
-          if (c0 + g < chunks) tmem_ld_32x32(tmem_base + uint32_t((c0 + g) * 32), v[g]);
+          if (c0 + g < chunks) tmem_ld_32x32(quarter + uint32_t((c0 + g) * 32), v[g]);
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           if (c0 + g < chunks) {
-            const uint32_t dst = slot + uint32_t((c0 + g) * 8 * 512);
+            const int c = c0 + g;
+            const int owner = c / own_chunks;
+            const uint32_t dst = map_to_cta(exch_addr, uint32_t(owner)) + mine +
+                                 uint32_t((c - owner * own_chunks) * 8 * R * 16);
 #pragma unroll
             for (int q = 0; q < 8; ++q)
-              st_cluster_v4(dst + uint32_t(q * 512), v[g][4 * q], v[g][4 * q + 1], v[g][4 * q + 2], v[g][4 * q + 3]);
+              st_cluster_v4(dst + uint32_t(q * R * 16), v[g][4 * q], v[g][4 * q + 1], v[g][4 * q + 2], v[g][4 * q + 3]);
           }
         }
       }
     }
   }
-  // Step 3: every slot is complete and visible to the leader.
+  // Step 3: every slot is complete and visible to its owner.
   __syncwarp();
   if (S > 1) cluster_sync_all(); else __syncthreads();
 
-  if (rank == 0 && *abort_flag == 0u) {
+  if (*abort_flag == 0u) {
     // ---------------------------------------------------------------- step 4: add, finish, store
-    // A thread owns row `lane` and takes groups of 8 columns (two 16-byte units of a slot): warp w
-    // the groups w, w + 4, ...  Reads of a slot are conflict-free (consecutive lanes, 16 bytes each).
+    // A thread takes (block of 32 rows, group of 8 columns) pairs: its lane is the row inside the
+    // block, so reads of a slot are conflict-free (consecutive lanes, 16 bytes each).
     const bool relu = (p.tail_flags & B200_LINEAR_RELU) != 0;
-    const int row = lane;
-    const float4* slots = reinterpret_cast<const float4*>(exch) + lane;
-    for (int g = warp; g < chunks * 4; g += 4) {
-      const int nc = n0 + g * 8;
-      if (nc >= p.N) break;
+    const int row_blocks = R / 32;
+    const int col0 = n0 + int(rank) * own_chunks * 32;  // first column this CTA finishes
+    const float4* slots = reinterpret_cast<const float4*>(exch);
+    for (int u = warp; u < row_blocks * own_chunks * 4; u += 4) {
+      const int rb = u % row_blocks, g = u / row_blocks;
+      const int row = rb * 32 + lane;
+      const int nc = col0 + g * 8;
+      if (nc >= p.N) continue;
       float x[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = 0.0f;
       for (int r = 0; r < S; ++r) {
-        const float4* part = slots + (r * (p.bn / 4) + g * 2) * 32;
-        const float4 t0 = part[0], t1 = part[32];
+        const float4* part = slots + (r * own_units + g * 2) * R + row;
+        const float4 t0 = part[0], t1 = part[R];
         if (r == 0) {
           x[0] = t0.x; x[1] = t0.y; x[2] = t0.z; x[3] = t0.w;
           x[4] = t1.x; x[5] = t1.y; x[6] = t1.z; x[7] = t1.w;
@@ -322,12 +334,15 @@ int read_and_clear_skinny_status(uint32_t* out) {
 // Decides whether the product is one this kernel should take and, if so, launches it.
 //   *used = false and B200_OK: not taken (the caller runs the general kernel).
 //   force = true: the caller insists (tile policy 3); a product that does not qualify is an error.
+// Costs are what one SM has to pull through its TMA unit, in 128-byte rows: per k-block the columns
+// of B (from DRAM) plus 0.3 x the rows of A (from L2, which was measured to weigh about that much).
 int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                        int64_t ldb, int64_t ldc, bool b_is_nk, const Tail& tail, int force_bn, bool force,
                        int64_t general_cost, cudaStream_t stream, bool* used) {
   *used = false;
-  if ((kind != KIND_F16 && kind != KIND_BF16) || M > kSkRows) {
-    if (force) return fail(B200_ERR_UNSUPPORTED, "the skinny kernel takes fp16 / bf16 products of at most %d rows", kSkRows);
+  if ((kind != KIND_F16 && kind != KIND_BF16) || M > kSkMaxRows) {
+    if (force)
+      return fail(B200_ERR_UNSUPPORTED, "the skinny kernel takes fp16 / bf16 products of at most %d rows", kSkMaxRows);
     return B200_OK;
   }
   int sms = 0;
@@ -335,14 +350,15 @@ int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t 
   B200_CUDA_TRY(cudaGetDevice(&dev));
   B200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int num_kb = int((K + kSkBK - 1) / kSkBK);
+  const int rows = int((M + 31) / 32) * 32;
 
-  // Tile width and cluster size: the smallest share of B per CTA (columns x k-blocks) among the
-  // configurations that run in one wave, with a small charge per extra range for the exchange.
+  // Tile width and cluster size: the smallest cost per CTA among the configurations that run in one
+  // wave, with a charge per split product for the exchange (about 1 us of streaming).
   int best_bn = 0, best_s = 0, best_per = 0, best_stages = 0;
   int64_t best_cost = 0;
   for (int bn = 128; bn <= 256; bn += 64) {
     if (force_bn && bn != force_bn) continue;
-    const int stage_bytes = kSkABytes + bn * 128;
+    const int stage_bytes = rows * 128 + bn * 128;
     const int64_t tiles = (N + bn - 1) / bn;
     if (tiles > sms) continue;
     int s_max = int(sms / tiles);
@@ -350,12 +366,12 @@ int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t 
     if (s_max > num_kb) s_max = num_kb;
     // Cluster sizes 1, 2, 4, 8 only: clusters of 3 did not all become resident together on a B200
     // (whatever the occupancy query said) and the product then took a second wave.
-    for (int s_try = s_max >= 8 ? 8 : (s_max >= 4 ? 4 : (s_max >= 2 ? 2 : 1)); s_try >= 1; s_try >>= 1) {
-      const int per = (num_kb + s_try - 1) / s_try;
-      const int s = (num_kb + per - 1) / per;  // no empty range
-      if (s & (s - 1)) continue;
-      // shared memory: ring, then s slots of 32 rows x bn fp32 in the exchange area; at least three stages
-      int stages = (kSkSmemBudget - 1024 - kSkTailBytes - s * bn * 128) / stage_bytes;
+    for (int s = s_max >= 8 ? 8 : (s_max >= 4 ? 4 : (s_max >= 2 ? 2 : 1)); s >= 1; s >>= 1) {
+      if ((bn / 32) % s) continue;  // the 32-column chunks are dealt out evenly
+      const int per = (num_kb + s - 1) / s;
+      if ((num_kb + per - 1) / per != s) continue;  // a range would be empty
+      // shared memory: ring, then rows x bn fp32 of exchange area; at least three stages
+      int stages = (kSkSmemBudget - 1024 - kSkTailBytes - bn * rows * 4) / stage_bytes;
       if (stages > kSkMaxStages) stages = kSkMaxStages;
       if (stages < 3) continue;
       if (s > 1) {
@@ -364,7 +380,7 @@ int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t 
         if (rc) return rc;
         if (resident < tiles) continue;  // a second wave of clusters would cost more than it saves
       }
-      const int64_t cost = int64_t(bn) * per + (s > 1 ? 384 : 0);  // the exchange is worth about 1 us of streaming
+      const int64_t cost = (int64_t(bn) * 10 + rows * 3) * per / 10 + (s > 1 ? 384 : 0);
       if (best_bn == 0 || cost < best_cost) {
         best_bn = bn; best_s = s; best_per = per; best_stages = stages; best_cost = cost;
       }
@@ -375,8 +391,12 @@ int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t 
     if (force) return fail(B200_ERR_UNSUPPORTED, "no one-wave configuration of the skinny kernel fits N = %lld", (long long)N);
     return B200_OK;
   }
-  // Not worth a different kernel unless every SM streams clearly less than it would in the general one.
-  if (!force && best_cost * 10 > general_cost * 9) return B200_OK;
+  // Not worth a different kernel unless every SM streams clearly less than it would in the general one:
+  // 10 % less for up to 64 rows.  With 96 or 128 rows the exchange area leaves a ring of three to five
+  // stages and A is as large as in the general kernel, which then streams faster per SM (M = 128,
+  // [4096 -> 11008]: 26.6 us there, 28.4 us here at 116 instead of 86 CTAs); such products come here
+  // only when the general tiling would leave more than half of the machine idle.
+  if (!force && (rows > 64 ? best_cost * 2 > general_cost : best_cost * 10 > general_cost * 9)) return B200_OK;
 
   if ((lda * 2) % 16 || (ldb * 2) % 16 || reinterpret_cast<uintptr_t>(A) % 16 || reinterpret_cast<uintptr_t>(B) % 16) {
     if (force) return fail(B200_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned A and B pointers and leading dimensions");
@@ -384,14 +404,14 @@ int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t 
   }
   if (reinterpret_cast<uintptr_t>(C) % 2) return fail(B200_ERR_UNSUPPORTED, "C is not aligned to its element size");
 
-  const int smem_bytes = best_stages * (kSkABytes + best_bn * 128) + best_s * best_bn * 128 + 1024 + kSkTailBytes;
+  const int smem_bytes = best_stages * (rows * 128 + best_bn * 128) + best_bn * rows * 4 + 1024 + kSkTailBytes;
   static thread_local int attr_dev = -1;
   if (dev != attr_dev) {
     B200_CUDA_TRY(cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemBudget));
     attr_dev = dev;
   }
   CUtensorMap ma, mb;
-  int rc = encode_operand_map(&ma, kind, A, M, K, lda, kSkBK, kSkRows, false);
+  int rc = encode_operand_map(&ma, kind, A, M, K, lda, kSkBK, rows, false);
   if (rc) return rc;
   rc = b_is_nk ? encode_operand_map(&mb, kind, B, N, K, ldb, kSkBK, best_bn, false)
                : encode_operand_map(&mb, kind, B, K, N, ldb, 64, kSkBK, false);
@@ -404,6 +424,7 @@ int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t 
   args.M = int(M);
   args.N = int(N);
   args.K = int(K);
+  args.rows = rows;
   args.bn = best_bn;
   args.splits = best_s;
   args.kb_per_split = best_per;

@@ -951,14 +951,16 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   }
   if (kind == KIND_I8 && !b_is_nk && bn < 128) bn = 128;  // an int8 span of N is 128 elements wide
 
-  // A 16-bit product of at most 32 rows streams B and little else.  If splitting K inside clusters
-  // lets every SM stream clearly less than the tiles chosen above would, that kernel takes it.
+  // A 16-bit product of at most 128 rows streams B and little else.  If splitting K inside clusters
+  // lets every SM pull clearly less through its TMA unit than the tiles chosen above would (columns
+  // of B per k-block, plus the 128 rows of A at the 0.3 they were measured to weigh, coming from L2),
+  // that kernel takes it.
   const bool nothing_forced = force_bn == 0 && g_force_bn == 0 && g_force_cg == 0 && g_force_splits == 0 &&
                               g_force_store == 0;
-  if (half_kind && n_dest == 1 && (skinny_forced || (nothing_forced && M <= 32))) {
+  if (half_kind && n_dest == 1 && (skinny_forced || (nothing_forced && M <= BM))) {
     const int64_t k_blocks = (K + 63) / 64;
     const int64_t tiles = int64_t(args.tiles_m) * ((N + bn - 1) / bn);
-    const int64_t general_cost = ((tiles + sms - 1) / sms) * bn * k_blocks;
+    const int64_t general_cost = ((tiles + sms - 1) / sms) * (int64_t(bn) * 10 + BM * 3) * k_blocks / 10;
     bool used = false;
     rc = launch_skinny_gemm(kind, A, B, C_list[0], M, N, K, lda, ldb, ldc, b_is_nk, tail, skinny_forced ? g_force_bn : 0,
                             skinny_forced, general_cost, stream, &used);

@@ -68,7 +68,7 @@ int b200_sm_count(void);
  * and a tile width of 64, 128 or 256 columns; `group_rows` (a multiple of 256) is how many rows
  * of C share one sweep across N in the tile order.  0 restores the automatic choice of each.
  * CTA pairs exist for 256-wide tiles only.  cta_group = 3 sends fp16 / bf16 products of at most
- * 32 rows to the K-split cluster kernel (tile_n 0, 128, 192 or 256) and makes every other product
+ * 128 rows to the K-split cluster kernel (tile_n 0, 128, 192 or 256) and makes every other product
  * fail with B200_ERR_UNSUPPORTED; without a policy that kernel is chosen by itself when it lets
  * every SM stream clearly less of B.  Integer results do not depend on the policy;
  * floating-point results may differ in the last bits (the order of the K blocks changes). */

@@ -1,4 +1,4 @@
-"""GPU parity tests of the K-split cluster kernel for skinny fp16 / bf16 products (at most 32 rows of A):
+"""GPU parity tests of the K-split cluster kernel for skinny fp16 / bf16 products (at most 128 rows of A):
 forced through tile policy 3 at every tile width, both layouts of B, ragged N and K, then as chosen
 automatically for the decode-shape linear layer.  Tolerances: fp16 <= 2e-3, bf16 <= 1e-2 relative
 Frobenius error against the unrounded fp32 sums of the one-thread-per-element kernel."""
@@ -19,7 +19,8 @@ def rel(a, b):
 
 
 SHAPES = [(16, 11008, 4096), (1, 4096, 4096), (32, 1000, 2176), (7, 264, 64), (32, 520, 200), (5, 1004, 512),
-          (31, 37000, 256), (16, 2048, 16384)]
+          (31, 37000, 256), (16, 2048, 16384), (33, 1000, 2176), (64, 4096, 4096), (100, 11008, 1024),
+          (128, 11008, 4096), (128, 520, 200), (96, 1004, 512)]
 
 
 @pytest.mark.parametrize("bn", [0, 128, 192, 256])
@@ -44,6 +45,11 @@ def test_skinny_kernel_forced(cb, device, policy, shape, b_is_nk, bn):
             st = capi.lib.b200_gemm_f16(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, 0, 0, 0, layout, None)
             assert st == 2
             continue
+        if M > 64 and bn == 256:  # 256 columns x 96 or 128 rows of exchange area leave no room for a ring
+            c = torch.empty((M, N), dtype=dt, device=device)
+            st = capi.lib.b200_gemm_f16(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, 0, 0, 0, layout, None)
+            assert st == 2
+            continue
         c1 = fn(a, b, layout)
         c2 = fn(a, b, layout)
         cb.check_device()
@@ -60,11 +66,11 @@ def test_skinny_kernel_refuses_what_it_was_not_built_for(cb, device, policy):
     from cudaintro_b200 import capi
 
     policy(3, 0, 0)
-    a = torch.zeros((33, 256), dtype=torch.float16, device=device)
+    a = torch.zeros((129, 256), dtype=torch.float16, device=device)
     b = torch.zeros((256, 512), dtype=torch.float16, device=device)
-    c = torch.zeros((33, 512), dtype=torch.float16, device=device)
+    c = torch.zeros((129, 512), dtype=torch.float16, device=device)
     lib = capi.lib
-    assert lib.b200_gemm_f16(a.data_ptr(), b.data_ptr(), c.data_ptr(), 33, 512, 256, 0, 0, 0, 0, None) == 2
+    assert lib.b200_gemm_f16(a.data_ptr(), b.data_ptr(), c.data_ptr(), 129, 512, 256, 0, 0, 0, 0, None) == 2
     a8 = torch.zeros((16, 256), dtype=torch.int8, device=device)
     b8 = torch.zeros((256, 512), dtype=torch.int8, device=device)
     c8 = torch.zeros((16, 512), dtype=torch.int32, device=device)
@@ -74,7 +80,7 @@ def test_skinny_kernel_refuses_what_it_was_not_built_for(cb, device, policy):
     torch.cuda.synchronize()
 
 
-@pytest.mark.parametrize("M", [1, 16, 32])
+@pytest.mark.parametrize("M", [1, 16, 32, 64])
 def test_decode_shape_linear_layer_takes_the_skinny_kernel_by_itself(cb, oracle, device, policy, M):
     """[4096 -> 11008] on a decode batch with nothing forced: the result must be the forced kernel's,
     bit for bit (the general kernel sums K in one piece and rounds differently somewhere in 11008 x M
