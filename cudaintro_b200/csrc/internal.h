@@ -42,7 +42,7 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
                            const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream,
                            const Tail& tail = Tail());
 
-// The same kind of product for at most 32 rows of 16-bit A: tiles shared by clusters that split K and
+// The same kind of product for at most 128 rows of 16-bit A: tiles shared by clusters that split K and
 // add their partial sums through distributed shared memory (gemm_skinny.cu).  *used tells whether the
 // kernel took the product; `general_cost` is what one SM would stream in the general kernel
 // (tile columns x k-blocks x waves), the yardstick it has to beat unless `force` is set.
