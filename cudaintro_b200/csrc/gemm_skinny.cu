@@ -1,5 +1,7 @@
 // Skinny tensor-core products for sm_100a: C[M,N] = A[M,K] * B with M <= 128 rows (a decode or
-// small-prefill batch against a wide weight matrix), fp16 / bf16 in and out, fp32 accumulation.
+// small-prefill batch against a wide weight matrix): fp16 / bf16 in and out with fp32 accumulation,
+// or int8 in with int32 accumulation and either int32 out or the per-row x per-column scaled bf16
+// output of the W8A8 product.
 //
 // Such a product streams B from HBM once and does little arithmetic, so what counts is that every
 // SM streams an equal share of B.  One SM cannot keep more than about 64 KB of TMA loads in flight,
@@ -47,7 +49,6 @@ __device__ uint32_t g_skinny_status = 0;  // bit 0: a bounded wait ran out somew
 
 constexpr int kSkThreads = 128;
 constexpr int kSkMaxRows = 128;          // rows of C one launch can produce
-constexpr int kSkBK = 64;                // 16-bit elements of K per stage (one 128-byte swizzle row)
 constexpr int kSkMaxStages = 8;
 constexpr int kSkSmemBudget = 227 * 1024;
 constexpr int kSkTailBytes = 256;        // barriers, TMEM slot, abort flag
@@ -61,11 +62,15 @@ struct SkinnyArgs {
   int splits;        // S: CTAs per cluster = K ranges per tile; divides bn / 32
   int kb_per_split;  // k-blocks per range (the last range may be shorter, never empty)
   int stages;
-  int kind;          // KIND_F16 or KIND_BF16
+  int kind;          // KIND_F16, KIND_BF16 or KIND_I8
+  int esz;           // bytes per element of A and B (2 or 1); a stage holds 128 bytes of K per row
+  int epi;           // Epilogue: EPI_F16, EPI_BF16, EPI_I32 or EPI_W8A8_BF16
   int b_is_nk;       // B is [N,K] (K contiguous) instead of [K,N]
   int vec_store;     // rows of C are 16-byte aligned
   const float* bias;
-  int tail_flags;    // b200_linear_flags
+  int tail_flags;    // b200_linear_flags (floating-point products)
+  const float* row_scale;  // W8A8
+  const float* col_scale;
 };
 
 __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -97,7 +102,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   const uint32_t rank = S > 1 ? cluster_cta_rank() : 0u;
   const int tile = int(blockIdx.x) / S;
   const int n0 = tile * p.bn;
-  const int num_kb = (p.K + kSkBK - 1) / kSkBK;
+  const int bk = 128 / p.esz;            // elements of K per stage (one 128-byte swizzle row)
+  const int span_cols = 128 / p.esz;     // columns in one 128-byte span of an N-contiguous B
+  const int span_bytes = bk * 128;       // one span: bk k-rows of 128 bytes
+  const int num_kb = (p.K + bk - 1) / bk;
   const int kb0 = int(rank) * p.kb_per_split;
   const int kb_count = min(p.kb_per_split, num_kb - kb0);  // >= 1 by construction of the launch
   const uint32_t tmem_cols = p.bn <= 128 ? 128u : 256u;
@@ -139,14 +147,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) break;
         uint8_t* sa = smem + stage * stage_bytes;
         uint8_t* sb = sa + a_bytes;
-        const int k = (kb0 + i) * kSkBK;
+        const int k = (kb0 + i) * bk;
         mbar_arrive_expect_tx(&full_bar[stage], uint32_t(stage_bytes));
         tma_load_2d(sa, &tmap_a, &full_bar[stage], k, 0);
         if (p.b_is_nk) {
           tma_load_2d(sb, &tmap_b, &full_bar[stage], k, n0);
         } else {
-          for (int s = 0; s < p.bn / 64; ++s)
-            tma_load_2d(sb + s * (kSkBK * 128), &tmap_b, &full_bar[stage], n0 + s * 64, k);
+          for (int s = 0; s < p.bn / span_cols; ++s)
+            tma_load_2d(sb + s * span_bytes, &tmap_b, &full_bar[stage], n0 + s * span_cols, k);
         }
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
       }
@@ -166,12 +174,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         const uint32_t sb = sa + uint32_t(a_bytes);
         const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
         const uint64_t b_desc = p.b_is_nk ? make_smem_desc_sw128(sb, 16, 1024)
-                                          : make_smem_desc_sw128(sb, kSkBK * 128, 1024);
+                                          : make_smem_desc_sw128(sb, uint32_t(span_bytes), 1024);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {  // 16 elements of K per instruction
+        for (int j = 0; j < 4; ++j) {  // 32 bytes of K per instruction
           const uint64_t a_adv = uint64_t((j * 32) >> 4);
-          const uint64_t b_adv = p.b_is_nk ? uint64_t((j * 32) >> 4) : uint64_t((j * 16 * 128) >> 4);
-          umma<KIND_F16>(tmem_base, a_desc + a_adv, b_desc + b_adv, idesc, (i | j) != 0 ? 1u : 0u);
+          const uint64_t b_adv = p.b_is_nk ? uint64_t((j * 32) >> 4) : uint64_t((j * (32 / p.esz) * 128) >> 4);
+          if (p.kind == KIND_I8)
+            umma<KIND_I8>(tmem_base, a_desc + a_adv, b_desc + b_adv, idesc, (i | j) != 0 ? 1u : 0u);
+          else
+            umma<KIND_F16>(tmem_base, a_desc + a_adv, b_desc + b_adv, idesc, (i | j) != 0 ? 1u : 0u);
         }
         umma_commit(&empty_bar[stage]);
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -224,54 +235,77 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     // A thread takes (block of 32 rows, group of 8 columns) pairs: its lane is the row inside the
     // block, so reads of a slot are conflict-free (consecutive lanes, 16 bytes each).
     const bool relu = (p.tail_flags & B200_LINEAR_RELU) != 0;
+    const bool integer = p.kind == KIND_I8;
+    const int out_bytes = p.epi == EPI_I32 ? 4 : 2;
     const int row_blocks = R / 32;
     const int col0 = n0 + int(rank) * own_chunks * 32;  // first column this CTA finishes
-    const float4* slots = reinterpret_cast<const float4*>(exch);
+    const uint4* slots = reinterpret_cast<const uint4*>(exch);
     for (int u = warp; u < row_blocks * own_chunks * 4; u += 4) {
       const int rb = u % row_blocks, g = u / row_blocks;
       const int row = rb * 32 + lane;
       const int nc = col0 + g * 8;
       if (nc >= p.N) continue;
-      float x[8];
+      uint32_t acc[8];  // int32 sums or fp32 sums, as bits
       for (int r = 0; r < S; ++r) {
-        const float4* part = slots + (r * own_units + g * 2) * R + row;
-        const float4 t0 = part[0], t1 = part[R];
-        if (r == 0) {
-          x[0] = t0.x; x[1] = t0.y; x[2] = t0.z; x[3] = t0.w;
-          x[4] = t1.x; x[5] = t1.y; x[6] = t1.z; x[7] = t1.w;
-        } else {
-          x[0] += t0.x; x[1] += t0.y; x[2] += t0.z; x[3] += t0.w;
-          x[4] += t1.x; x[5] += t1.y; x[6] += t1.z; x[7] += t1.w;
+        const uint4* part = slots + (r * own_units + g * 2) * R + row;
+        const uint4 t0 = part[0], t1 = part[R];
+        const uint32_t in[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (r == 0) acc[j] = in[j];
+          else if (integer) acc[j] += in[j];
+          else acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __uint_as_float(in[j]));
         }
       }
-      uint32_t w[4];
+      uint32_t w[8];  // 8 outputs: 8 words of int32, or 4 words of two 16-bit values
+      if (p.epi == EPI_I32) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float x0 = x[2 * j], x1 = x[2 * j + 1];
-        if (p.bias != nullptr) {
-          x0 += __ldg(p.bias + min(nc + 2 * j, p.N - 1));
-          x1 += __ldg(p.bias + min(nc + 2 * j + 1, p.N - 1));
-        }
-        if (relu) {
-          x0 = fmaxf(0.0f, x0);
-          x1 = fmaxf(0.0f, x1);
-        }
-        if (p.kind == KIND_F16) {
-          __half2 h = __floats2half2_rn(x0, x1);
-          w[j] = *reinterpret_cast<uint32_t*>(&h);
-        } else {
-          __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-          w[j] = *reinterpret_cast<uint32_t*>(&h);
+        for (int j = 0; j < 8; ++j) w[j] = acc[j];
+      } else {
+        const float rs = (p.epi == EPI_W8A8_BF16 && row < p.M) ? __ldg(p.row_scale + row) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float x0, x1;
+          if (p.epi == EPI_W8A8_BF16) {
+            // (float(acc) * row_scale) * col_scale, each step rounded once, then to bf16
+            const float c0 = __ldg(p.col_scale + min(nc + 2 * j, p.N - 1));
+            const float c1 = __ldg(p.col_scale + min(nc + 2 * j + 1, p.N - 1));
+            x0 = __fmul_rn(__fmul_rn(__int2float_rn(int(acc[2 * j])), rs), c0);
+            x1 = __fmul_rn(__fmul_rn(__int2float_rn(int(acc[2 * j + 1])), rs), c1);
+          } else {
+            x0 = __uint_as_float(acc[2 * j]);
+            x1 = __uint_as_float(acc[2 * j + 1]);
+            if (p.bias != nullptr) {
+              x0 += __ldg(p.bias + min(nc + 2 * j, p.N - 1));
+              x1 += __ldg(p.bias + min(nc + 2 * j + 1, p.N - 1));
+            }
+            if (relu) {
+              x0 = fmaxf(0.0f, x0);
+              x1 = fmaxf(0.0f, x1);
+            }
+          }
+          if (p.epi == EPI_F16) {
+            __half2 h = __floats2half2_rn(x0, x1);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
         }
       }
       if (row < p.M) {
-        uint16_t* dst = static_cast<uint16_t*>(p.C) + int64_t(row) * p.ldc + nc;
+        char* dst = static_cast<char*>(p.C) + (int64_t(row) * p.ldc + nc) * out_bytes;
         if (p.vec_store && nc + 8 <= p.N) {
           *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+          if (out_bytes == 4) *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+        } else if (out_bytes == 4) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (nc + j < p.N) reinterpret_cast<uint32_t*>(dst)[j] = w[j];
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            if (nc + j < p.N) dst[j] = uint16_t(w[j >> 1] >> ((j & 1) * 16));
+            if (nc + j < p.N) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(w[j >> 1] >> ((j & 1) * 16));
         }
       }
     }
@@ -336,20 +370,27 @@ int read_and_clear_skinny_status(uint32_t* out) {
 //   force = true: the caller insists (tile policy 3); a product that does not qualify is an error.
 // Costs are what one SM has to pull through its TMA unit, in 128-byte rows: per k-block the columns
 // of B (from DRAM) plus 0.3 x the rows of A (from L2, which was measured to weigh about that much).
-int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                       int64_t ldb, int64_t ldc, bool b_is_nk, const Tail& tail, int force_bn, bool force,
-                       int64_t general_cost, cudaStream_t stream, bool* used) {
+int launch_skinny_gemm(int kind, int epi, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                       int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, const float* row_scale,
+                       const float* col_scale, const Tail& tail, int force_bn, bool force, int64_t general_cost,
+                       cudaStream_t stream, bool* used) {
   *used = false;
-  if ((kind != KIND_F16 && kind != KIND_BF16) || M > kSkMaxRows) {
+  const bool known = (kind == KIND_F16 && epi == EPI_F16) || (kind == KIND_BF16 && epi == EPI_BF16) ||
+                     (kind == KIND_I8 && (epi == EPI_I32 || epi == EPI_W8A8_BF16));
+  if (!known || M > kSkMaxRows) {
     if (force)
-      return fail(B200_ERR_UNSUPPORTED, "the skinny kernel takes fp16 / bf16 products of at most %d rows", kSkMaxRows);
+      return fail(B200_ERR_UNSUPPORTED, "the skinny kernel takes fp16, bf16 and int8 products of at most %d rows",
+                  kSkMaxRows);
     return B200_OK;
   }
+  const int esz = kind == KIND_I8 ? 1 : 2;
+  const int out_esz = epi == EPI_I32 ? 4 : 2;
+  const int bk = 128 / esz;
   int sms = 0;
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
   B200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int num_kb = int((K + kSkBK - 1) / kSkBK);
+  const int num_kb = int((K + bk - 1) / bk);
   const int rows = int((M + 31) / 32) * 32;
 
   // Tile width and cluster size: the smallest cost per CTA among the configurations that run in one
@@ -358,6 +399,7 @@ int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t 
   int64_t best_cost = 0;
   for (int bn = 128; bn <= 256; bn += 64) {
     if (force_bn && bn != force_bn) continue;
+    if (!b_is_nk && bn % (128 / esz)) continue;  // an N-contiguous B is staged in whole 128-byte spans
     const int stage_bytes = rows * 128 + bn * 128;
     const int64_t tiles = (N + bn - 1) / bn;
     if (tiles > sms) continue;
@@ -396,13 +438,16 @@ int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t 
   // stages and A is as large as in the general kernel, which then streams faster per SM (M = 128,
   // [4096 -> 11008]: 26.6 us there, 28.4 us here at 116 instead of 86 CTAs); such products come here
   // only when the general tiling would leave more than half of the machine idle.
-  if (!force && (rows > 64 ? best_cost * 2 > general_cost : best_cost * 10 > general_cost * 9)) return B200_OK;
+  // Without a split this kernel has nothing over the general one (which streams a little faster per SM).
+  if (!force && (best_s == 1 || (rows > 64 ? best_cost * 2 > general_cost : best_cost * 10 > general_cost * 9)))
+    return B200_OK;
 
-  if ((lda * 2) % 16 || (ldb * 2) % 16 || reinterpret_cast<uintptr_t>(A) % 16 || reinterpret_cast<uintptr_t>(B) % 16) {
+  if ((lda * esz) % 16 || (ldb * esz) % 16 || reinterpret_cast<uintptr_t>(A) % 16 || reinterpret_cast<uintptr_t>(B) % 16) {
     if (force) return fail(B200_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned A and B pointers and leading dimensions");
     return B200_OK;  // the general path reports it
   }
-  if (reinterpret_cast<uintptr_t>(C) % 2) return fail(B200_ERR_UNSUPPORTED, "C is not aligned to its element size");
+  if (reinterpret_cast<uintptr_t>(C) % out_esz) return fail(B200_ERR_UNSUPPORTED, "C is not aligned to its element size");
+  if (epi == EPI_W8A8_BF16 && (!row_scale || !col_scale)) return fail(B200_ERR_BAD_ARGUMENT, "null scale pointer");
 
   const int smem_bytes = best_stages * (rows * 128 + best_bn * 128) + best_bn * rows * 4 + 1024 + kSkTailBytes;
   static thread_local int attr_dev = -1;
@@ -411,10 +456,10 @@ int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t 
     attr_dev = dev;
   }
   CUtensorMap ma, mb;
-  int rc = encode_operand_map(&ma, kind, A, M, K, lda, kSkBK, rows, false);
+  int rc = encode_operand_map(&ma, kind, A, M, K, lda, bk, rows, false);
   if (rc) return rc;
-  rc = b_is_nk ? encode_operand_map(&mb, kind, B, N, K, ldb, kSkBK, best_bn, false)
-               : encode_operand_map(&mb, kind, B, K, N, ldb, 64, kSkBK, false);
+  rc = b_is_nk ? encode_operand_map(&mb, kind, B, N, K, ldb, bk, best_bn, false)
+               : encode_operand_map(&mb, kind, B, K, N, ldb, 128 / esz, bk, false);
   if (rc) return rc;
 
   SkinnyArgs args;
@@ -430,10 +475,14 @@ int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t 
   args.kb_per_split = best_per;
   args.stages = best_stages;
   args.kind = kind;
+  args.esz = esz;
+  args.epi = epi;
   args.b_is_nk = b_is_nk ? 1 : 0;
-  args.vec_store = ((ldc * 2) % 16 == 0 && reinterpret_cast<uintptr_t>(C) % 16 == 0) ? 1 : 0;
+  args.vec_store = ((ldc * out_esz) % 16 == 0 && reinterpret_cast<uintptr_t>(C) % 16 == 0) ? 1 : 0;
   args.bias = tail.bias;
   args.tail_flags = tail.flags;
+  args.row_scale = row_scale;
+  args.col_scale = col_scale;
 
   const int tiles = int((N + best_bn - 1) / best_bn);
   cudaLaunchConfig_t cfg = {};

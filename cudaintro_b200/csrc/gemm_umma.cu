@@ -927,9 +927,9 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   int rc = sm_count_of_current_device(&sms);
   if (rc) return rc;
   const bool skinny_forced = g_force_cg == 3;  // tile policy 3: the K-split cluster kernel or nothing
-  const bool half_kind = kind == KIND_F16 || kind == KIND_BF16;
-  if (skinny_forced && !(half_kind && n_dest == 1))
-    return fail(B200_ERR_UNSUPPORTED, "the skinny kernel takes fp16 / bf16 products with one destination");
+  const bool skinny_kind = kind == KIND_F16 || kind == KIND_BF16 || kind == KIND_I8;
+  if (skinny_forced && !(skinny_kind && n_dest == 1))
+    return fail(B200_ERR_UNSUPPORTED, "the skinny kernel takes fp16, bf16 and int8 products with one destination");
   int bn = force_bn ? force_bn : (skinny_forced ? 0 : g_force_bn);
   int cg = skinny_forced ? 1 : g_force_cg;
   if (cg == 0) {
@@ -951,19 +951,19 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   }
   if (kind == KIND_I8 && !b_is_nk && bn < 128) bn = 128;  // an int8 span of N is 128 elements wide
 
-  // A 16-bit product of at most 128 rows streams B and little else.  If splitting K inside clusters
+  // A product of at most 128 rows streams B and little else.  If splitting K inside clusters
   // lets every SM pull clearly less through its TMA unit than the tiles chosen above would (columns
   // of B per k-block, plus the 128 rows of A at the 0.3 they were measured to weigh, coming from L2),
   // that kernel takes it.
   const bool nothing_forced = force_bn == 0 && g_force_bn == 0 && g_force_cg == 0 && g_force_splits == 0 &&
                               g_force_store == 0;
-  if (half_kind && n_dest == 1 && (skinny_forced || (nothing_forced && M <= BM))) {
-    const int64_t k_blocks = (K + 63) / 64;
+  if (skinny_kind && n_dest == 1 && (skinny_forced || (nothing_forced && M <= BM))) {
+    const int64_t k_blocks = (K * elem + 127) / 128;
     const int64_t tiles = int64_t(args.tiles_m) * ((N + bn - 1) / bn);
     const int64_t general_cost = ((tiles + sms - 1) / sms) * (int64_t(bn) * 10 + BM * 3) * k_blocks / 10;
     bool used = false;
-    rc = launch_skinny_gemm(kind, A, B, C_list[0], M, N, K, lda, ldb, ldc, b_is_nk, tail, skinny_forced ? g_force_bn : 0,
-                            skinny_forced, general_cost, stream, &used);
+    rc = launch_skinny_gemm(kind, epi, A, B, C_list[0], M, N, K, lda, ldb, ldc, b_is_nk, row_scale, col_scale, tail,
+                            skinny_forced ? g_force_bn : 0, skinny_forced, general_cost, stream, &used);
     if (rc || used) return rc;
   }
 

@@ -42,13 +42,15 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
                            const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream,
                            const Tail& tail = Tail());
 
-// The same kind of product for at most 128 rows of 16-bit A: tiles shared by clusters that split K and
-// add their partial sums through distributed shared memory (gemm_skinny.cu).  *used tells whether the
+// The same kind of product for at most 128 rows of A (fp16, bf16, or int8 with the int32 or the W8A8
+// epilogue): tiles shared by clusters that split K and add their partial sums through distributed
+// shared memory (gemm_skinny.cu).  *used tells whether the
 // kernel took the product; `general_cost` is what one SM would stream in the general kernel
 // (tile columns x k-blocks x waves), the yardstick it has to beat unless `force` is set.
-int launch_skinny_gemm(int kind, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                       int64_t ldb, int64_t ldc, bool b_is_nk, const Tail& tail, int force_bn, bool force,
-                       int64_t general_cost, cudaStream_t stream, bool* used);
+int launch_skinny_gemm(int kind, int epi, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                       int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, const float* row_scale,
+                       const float* col_scale, const Tail& tail, int force_bn, bool force, int64_t general_cost,
+                       cudaStream_t stream, bool* used);
 int read_and_clear_skinny_status(uint32_t* out);
 
 // 2-D tensor map over a row-major [rows, cols] matrix of MmaKind `kind` elements with leading

@@ -163,6 +163,36 @@ def case_w8a8(M=8192, N=28672, K=8192):
     return run
 
 
+def case_w8a8_decode(M, K=4096, N=11008):
+    """int8 activations [M,K] times int8 weights [K,N] with per-row x per-column scales, bf16 out: the
+    quantised form of the decode-shape linear layer.  Weight copies are rotated so that they come from DRAM."""
+    def run(args, device):
+        import torch
+
+        import cudaintro_b200 as cb
+
+        x = _randint8((M, K), device, 1)
+        copies = int(L2_BYTES * 3 // (K * N)) + 1
+        ws = [_randint8((K, N), device, 10 + i) for i in range(copies)]
+        rs = torch.rand(M, device=device) * 0.01 + 0.001
+        cs = torch.rand(N, device=device) * 0.01 + 0.001
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        state = {"i": 0}
+
+        def fn():
+            cb.gemm_w8a8_bf16(x, ws[state["i"] % copies], rs, cs, out=out)
+            state["i"] += 1
+
+        med, best = _time(fn, max(args.reps, copies), max(args.warmup, copies))
+        cb.check_device()
+        byts = M * K + K * N + 2 * M * N + 4 * (M + N)
+        hbm, _, src = _peaks()
+        return {"bound": "hbm", "ms_median": med, "ms_best": best, "algorithmic_bytes": byts,
+                "weight_copies_rotated": copies, "achieved": byts / (med * 1e-3) / 1e9, "unit": "GB/s", "peak": hbm,
+                "peak_source": f"{src} HBM copy", "frac": byts / (med * 1e-3) / 1e9 / hbm}
+    return run
+
+
 def case_f32(n, mode_name):
     def run(args, device):
         import torch
@@ -249,6 +279,8 @@ CASES = {
     "bf16_4096_colmajor": case_gemm("bf16", 4096, 4096, 4096, "COL_MAJOR_NN"),
     "fp16_4096_colmajor": case_gemm("f16", 4096, 4096, 4096, "COL_MAJOR_NN"),
     "w8a8": case_w8a8(),
+    "w8a8_decode_m16": case_w8a8_decode(16),
+    "w8a8_decode_m128": case_w8a8_decode(128),
     "linear_m16": case_linear(16),
     "linear_m128": case_linear(128),
     "linear_m1024": case_linear(1024),

@@ -1,7 +1,8 @@
-"""GPU parity tests of the K-split cluster kernel for skinny fp16 / bf16 products (at most 128 rows of A):
-forced through tile policy 3 at every tile width, both layouts of B, ragged N and K, then as chosen
-automatically for the decode-shape linear layer.  Tolerances: fp16 <= 2e-3, bf16 <= 1e-2 relative
-Frobenius error against the unrounded fp32 sums of the one-thread-per-element kernel."""
+"""GPU parity tests of the K-split cluster kernel for skinny products (at most 128 rows of A): forced
+through tile policy 3 at every tile width, both layouts of B, ragged N and K, then as chosen
+automatically for the decode-shape linear layer.  int8 -> int32 and W8A8 -> bf16 are bit-exact (which
+checks the exchange of partial sums between the CTAs of a cluster to the last bit); fp16 <= 2e-3 and
+bf16 <= 1e-2 relative Frobenius error against the unrounded fp32 sums of the one-thread-per-element kernel."""
 import numpy as np
 import pytest
 
@@ -61,6 +62,41 @@ def test_skinny_kernel_forced(cb, device, policy, shape, b_is_nk, bn):
         assert rel(c1, general) <= tol / 2
 
 
+@pytest.mark.parametrize("bn", [0, 128, 192, 256])
+@pytest.mark.parametrize("b_is_nk", [False, True])
+@pytest.mark.parametrize("shape", [(16, 11008, 4096), (1, 4096, 4096), (32, 1008, 2176), (7, 272, 128), (33, 1040, 8192),
+                                   (64, 4096, 4096), (128, 11008, 1024), (128, 528, 208), (96, 1004, 512)])
+def test_skinny_kernel_forced_int8_and_w8a8_bit_exact(cb, device, policy, shape, b_is_nk, bn):
+    import torch
+    from cudaintro_b200 import capi
+
+    M, N, K = shape
+    if not b_is_nk and N % 16:
+        pytest.skip("rows of an int8 [K, N] matrix must be 16-byte multiples")
+    layout = cb.ROW_MAJOR_BT if b_is_nk else cb.ROW_MAJOR
+    g = torch.Generator(device=device).manual_seed(M * 17 + N + K + bn)
+    a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=device, generator=g)
+    b = torch.randint(-127, 128, (N, K) if b_is_nk else (K, N), dtype=torch.int8, device=device, generator=g)
+    want = cb.gemm_naive(a, b, layout)
+    policy(3, bn, 0)
+    feasible = not (M > 64 and bn == 256) and not (not b_is_nk and bn == 192)  # int8 spans of N are 128 columns wide
+    if not feasible:
+        c = torch.empty((M, N), dtype=torch.int32, device=device)
+        assert capi.lib.b200_gemm_i8_i32(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, 0, 0, 0, layout, None) == 2
+        return
+    for _ in range(2):
+        c = cb.gemm_i8_i32(a, b, layout)
+        cb.check_device()
+        assert torch.equal(c, want)
+    if not b_is_nk:
+        rs = torch.rand(M, device=device, generator=g) * 0.01 + 0.001
+        cs = torch.rand(N, device=device, generator=g) * 0.01 + 0.001
+        cw = cb.gemm_w8a8_bf16(a, b, rs, cs)
+        cb.check_device()
+        want_w = ((want.float() * rs[:, None]) * cs[None, :]).to(torch.bfloat16)
+        assert torch.equal(cw.view(torch.int16), want_w.view(torch.int16))
+
+
 def test_skinny_kernel_refuses_what_it_was_not_built_for(cb, device, policy):
     import torch
     from cudaintro_b200 import capi
@@ -71,12 +107,13 @@ def test_skinny_kernel_refuses_what_it_was_not_built_for(cb, device, policy):
     c = torch.zeros((129, 512), dtype=torch.float16, device=device)
     lib = capi.lib
     assert lib.b200_gemm_f16(a.data_ptr(), b.data_ptr(), c.data_ptr(), 129, 512, 256, 0, 0, 0, 0, None) == 2
-    a8 = torch.zeros((16, 256), dtype=torch.int8, device=device)
-    b8 = torch.zeros((256, 512), dtype=torch.int8, device=device)
-    c8 = torch.zeros((16, 512), dtype=torch.int32, device=device)
-    assert lib.b200_gemm_i8_i32(a8.data_ptr(), b8.data_ptr(), c8.data_ptr(), 16, 512, 256, 0, 0, 0, 0, None) == 2
+    a32 = torch.zeros((16, 256), dtype=torch.float32, device=device)
+    b32 = torch.zeros((256, 512), dtype=torch.float32, device=device)
+    c32 = torch.zeros((16, 512), dtype=torch.float32, device=device)
+    args32 = (a32.data_ptr(), b32.data_ptr(), c32.data_ptr(), 16, 512, 256, 0, 0, 0, 0, cb.F32_TF32, None)
+    assert lib.b200_gemm_f32(*args32) == 2  # no tf32 variant of the skinny kernel
     policy(0, 0, 0)
-    assert lib.b200_gemm_i8_i32(a8.data_ptr(), b8.data_ptr(), c8.data_ptr(), 16, 512, 256, 0, 0, 0, 0, None) == 0
+    assert lib.b200_gemm_f32(*args32) == 0
     torch.cuda.synchronize()
 
 
