@@ -4,9 +4,11 @@
 // output of the W8A8 product.
 //
 // Such a product streams B from HBM once and does little arithmetic, so what counts is that every
-// SM streams an equal share of B.  One SM cannot keep more than about 64 KB of TMA loads in flight,
-// which from DRAM is 50-60 GB/s: a [4096 -> 11008] layer cut into 86 column tiles of 128 therefore
-// runs at the speed of 86 SMs however deep the ring is.  Here a tile of BN columns (128, 192 or 256)
+// SM streams an equal share of B.  A CTA of this kind completes one k-block (128 bytes of K per row)
+// about every 0.36 us whether its tile is 128 or 192 columns wide and however deep its ring is (the
+// pace of the serial TMA-issue and MMA-issue loops), i.e. 45-70 GB/s per SM: a [4096 -> 11008] layer
+// cut into 86 column tiles of 128 therefore runs at the speed of 86 SMs, 3.6 TB/s, while 116 CTAs of
+// 192 columns reach the 7 TB/s HBM gives.  Here a tile of BN columns (128, 192 or 256)
 // is shared by a thread-block cluster of S CTAs (1, 2, 4 or 8) that each stream one K range of it;
 // tiles x S is chosen close to the SM count.  The partial sums meet on chip, reduce-scatter fashion:
 //
@@ -78,6 +80,12 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a,
                : "memory");
 }
 
+// ESZ (bytes per element of A and B) and B_NK (B given as [N,K]) are template parameters although the
+// code would run with them as arguments: the TMA-issuing lane and the MMA-issuing lane each execute a
+// short serial loop per k-block that paces the whole CTA, and every instruction in those loops shows in
+// the result (an integer division per iteration doubled the time of the kernel; run-time strides and
+// a run-time choice of the MMA kind cost another 10 %).
+template <int ESZ, bool B_NK>
 __global__ void __launch_bounds__(kSkThreads, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                    const SkinnyArgs p) {
@@ -102,9 +110,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   const uint32_t rank = S > 1 ? cluster_cta_rank() : 0u;
   const int tile = int(blockIdx.x) / S;
   const int n0 = tile * p.bn;
-  const int bk = 128 / p.esz;            // elements of K per stage (one 128-byte swizzle row)
-  const int span_cols = 128 / p.esz;     // columns in one 128-byte span of an N-contiguous B
-  const int span_bytes = bk * 128;       // one span: bk k-rows of 128 bytes
+  constexpr int bk = 128 / ESZ;          // elements of K per stage (one 128-byte swizzle row)
+  constexpr int span_cols = 128 / ESZ;   // columns in one 128-byte span of an N-contiguous B
+  constexpr int span_bytes = bk * 128;   // one span: bk k-rows of 128 bytes
+  const int nspans = p.bn / span_cols;   // spans of an N-contiguous B tile
   const int num_kb = (p.K + bk - 1) / bk;
   const int kb0 = int(rank) * p.kb_per_split;
   const int kb_count = min(p.kb_per_split, num_kb - kb0);  // >= 1 by construction of the launch
@@ -150,10 +159,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         const int k = (kb0 + i) * bk;
         mbar_arrive_expect_tx(&full_bar[stage], uint32_t(stage_bytes));
         tma_load_2d(sa, &tmap_a, &full_bar[stage], k, 0);
-        if (p.b_is_nk) {
+        if constexpr (B_NK) {
           tma_load_2d(sb, &tmap_b, &full_bar[stage], k, n0);
         } else {
-          for (int s = 0; s < p.bn / span_cols; ++s)
+          for (int s = 0; s < nspans; ++s)
             tma_load_2d(sb + s * span_bytes, &tmap_b, &full_bar[stage], n0 + s * span_cols, k);
         }
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -163,7 +172,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_instr_desc(p.kind, 128, p.bn, 0, p.b_is_nk ? 0 : 1);
+      const uint32_t idesc = make_instr_desc(p.kind, 128, p.bn, 0, B_NK ? 0 : 1);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -173,16 +182,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         const uint32_t sa = smem_u32(smem + stage * stage_bytes);
         const uint32_t sb = sa + uint32_t(a_bytes);
         const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
-        const uint64_t b_desc = p.b_is_nk ? make_smem_desc_sw128(sb, 16, 1024)
-                                          : make_smem_desc_sw128(sb, uint32_t(span_bytes), 1024);
+        const uint64_t b_desc = B_NK ? make_smem_desc_sw128(sb, 16, 1024)
+                                     : make_smem_desc_sw128(sb, uint32_t(span_bytes), 1024);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {  // 32 bytes of K per instruction
           const uint64_t a_adv = uint64_t((j * 32) >> 4);
-          const uint64_t b_adv = p.b_is_nk ? uint64_t((j * 32) >> 4) : uint64_t((j * (32 / p.esz) * 128) >> 4);
-          if (p.kind == KIND_I8)
-            umma<KIND_I8>(tmem_base, a_desc + a_adv, b_desc + b_adv, idesc, (i | j) != 0 ? 1u : 0u);
-          else
-            umma<KIND_F16>(tmem_base, a_desc + a_adv, b_desc + b_adv, idesc, (i | j) != 0 ? 1u : 0u);
+          // 32 bytes along a K-contiguous row, or the k-rows of an N-contiguous span that hold 32 bytes of K
+          const uint64_t b_adv = B_NK ? uint64_t((j * 32) >> 4) : uint64_t((j * (32 / ESZ) * 128) >> 4);
+          umma<(ESZ == 1 ? KIND_I8 : KIND_F16)>(tmem_base, a_desc + a_adv, b_desc + b_adv, idesc,
+                                                (i | j) != 0 ? 1u : 0u);
         }
         umma_commit(&empty_bar[stage]);
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -328,6 +336,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   }
 }
 
+using SkinnyKernel = void (*)(const CUtensorMap, const CUtensorMap, const SkinnyArgs);
+SkinnyKernel skinny_kernel_for(int esz, bool b_is_nk) {
+  if (esz == 1) return b_is_nk ? gemm_skinny_kernel<1, true> : gemm_skinny_kernel<1, false>;
+  return b_is_nk ? gemm_skinny_kernel<2, true> : gemm_skinny_kernel<2, false>;
+}
+
 // Clusters of `splits` CTAs the device can hold at once.  Every configuration takes more than half
 // of an SM's shared memory, so one CTA per SM it is; the query is made with the largest footprint.
 int max_resident_clusters(int splits, int* out) {
@@ -349,8 +363,10 @@ int max_resident_clusters(int splits, int* out) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  B200_CUDA_TRY(cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemBudget));
-  B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, gemm_skinny_kernel, &cfg));
+  // the four instantiations have the same footprint (one CTA per SM): ask for one of them
+  SkinnyKernel probe = skinny_kernel_for(2, false);
+  B200_CUDA_TRY(cudaFuncSetAttribute(probe, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemBudget));
+  B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, probe, &cfg));
   if (dev < 64) cache[dev][splits] = n > 0 ? n : -1;
   *out = n;
   return B200_OK;
@@ -410,6 +426,7 @@ int launch_skinny_gemm(int kind, int epi, const void* A, const void* B, void* C,
     // (whatever the occupancy query said) and the product then took a second wave.
     for (int s = s_max >= 8 ? 8 : (s_max >= 4 ? 4 : (s_max >= 2 ? 2 : 1)); s >= 1; s >>= 1) {
       if ((bn / 32) % s) continue;  // the 32-column chunks are dealt out evenly
+      if (s == 1 && !force) continue;  // without a split this kernel has nothing over the general one
       const int per = (num_kb + s - 1) / s;
       if ((num_kb + per - 1) / per != s) continue;  // a range would be empty
       // shared memory: ring, then rows x bn fp32 of exchange area; at least three stages
@@ -438,9 +455,7 @@ int launch_skinny_gemm(int kind, int epi, const void* A, const void* B, void* C,
   // stages and A is as large as in the general kernel, which then streams faster per SM (M = 128,
   // [4096 -> 11008]: 26.6 us there, 28.4 us here at 116 instead of 86 CTAs); such products come here
   // only when the general tiling would leave more than half of the machine idle.
-  // Without a split this kernel has nothing over the general one (which streams a little faster per SM).
-  if (!force && (best_s == 1 || (rows > 64 ? best_cost * 2 > general_cost : best_cost * 10 > general_cost * 9)))
-    return B200_OK;
+  if (!force && (rows > 64 ? best_cost * 2 > general_cost : best_cost * 10 > general_cost * 9)) return B200_OK;
 
   if ((lda * esz) % 16 || (ldb * esz) % 16 || reinterpret_cast<uintptr_t>(A) % 16 || reinterpret_cast<uintptr_t>(B) % 16) {
     if (force) return fail(B200_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned A and B pointers and leading dimensions");
@@ -450,10 +465,13 @@ int launch_skinny_gemm(int kind, int epi, const void* A, const void* B, void* C,
   if (epi == EPI_W8A8_BF16 && (!row_scale || !col_scale)) return fail(B200_ERR_BAD_ARGUMENT, "null scale pointer");
 
   const int smem_bytes = best_stages * (rows * 128 + best_bn * 128) + best_bn * rows * 4 + 1024 + kSkTailBytes;
-  static thread_local int attr_dev = -1;
-  if (dev != attr_dev) {
-    B200_CUDA_TRY(cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemBudget));
-    attr_dev = dev;
+  SkinnyKernel kernel = skinny_kernel_for(esz, b_is_nk);
+  // The shared-memory attribute is per device and per instantiation.
+  static thread_local int attr_dev[4] = {-1, -1, -1, -1};
+  const int which = (esz == 1 ? 2 : 0) + (b_is_nk ? 1 : 0);
+  if (dev != attr_dev[which]) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkSmemBudget));
+    attr_dev[which] = dev;
   }
   CUtensorMap ma, mb;
   int rc = encode_operand_map(&ma, kind, A, M, K, lda, bk, rows, false);
@@ -506,7 +524,7 @@ int launch_skinny_gemm(int kind, int epi, const void* A, const void* B, void* C,
   }
   cfg.attrs = attr;
   cfg.numAttrs = unsigned(nattr);
-  B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_skinny_kernel, ma, mb, args));
+  B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ma, mb, args));
   *used = true;
   return B200_OK;
 }
