@@ -173,17 +173,19 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_instr_desc(p.kind, 128, p.bn, 0, B_NK ? 0 : 1);
+      // descriptors of stage 0, stepped per k-block (the address field is in units of 16 bytes)
+      const uint32_t ring = smem_u32(smem);
+      const uint64_t a_desc0 = make_smem_desc_sw128(ring, 16, 1024);
+      const uint64_t b_desc0 = B_NK ? make_smem_desc_sw128(ring + uint32_t(a_bytes), 16, 1024)
+                                    : make_smem_desc_sw128(ring + uint32_t(a_bytes), uint32_t(span_bytes), 1024);
+      const uint64_t stage_step = uint64_t(stage_bytes >> 4);
+      uint64_t a_desc = a_desc0, b_desc = b_desc0;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int i = 0; i < kb_count; ++i) {
         if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t sa = smem_u32(smem + stage * stage_bytes);
-        const uint32_t sb = sa + uint32_t(a_bytes);
-        const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
-        const uint64_t b_desc = B_NK ? make_smem_desc_sw128(sb, 16, 1024)
-                                     : make_smem_desc_sw128(sb, uint32_t(span_bytes), 1024);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {  // 32 bytes of K per instruction
           const uint64_t a_adv = uint64_t((j * 32) >> 4);
@@ -193,7 +195,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                                                 (i | j) != 0 ? 1u : 0u);
         }
         umma_commit(&empty_bar[stage]);
-        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        a_desc += stage_step;
+        b_desc += stage_step;
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; a_desc = a_desc0; b_desc = b_desc0; }
       }
       if (ok) umma_commit(acc_full);
     }

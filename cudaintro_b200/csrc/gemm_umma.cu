@@ -357,6 +357,18 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && cta_rank == 0) {
       constexpr uint32_t idesc = make_instr_desc(KIND, TILE_M, BN, 0, B_NK ? 0 : 1);
+      // Operand descriptors of stage 0; a later stage's differ in the address field only, which is in
+      // units of 16 bytes and cannot carry out of its 14 bits for addresses inside shared memory.  This
+      // lane's loop feeds the tensor pipe, so the descriptors are stepped, not rebuilt, per k-block.
+      const uint32_t ring = smem_u32(smem);
+      const uint64_t a_desc0 = make_smem_desc_sw128(ring, 16, 1024);
+      // An N-contiguous operand of 32-bit elements only exists in the "128-byte swizzle on
+      // 32-byte chunks" form: atoms of 128 bytes of N by 4 k-rows (512 bytes).
+      const uint64_t b_desc0 = B_NK ? make_smem_desc_sw128(ring + T::A_BYTES, 16, 1024)
+                               : (KIND == KIND_TF32 ? make_smem_desc(ring + T::A_BYTES, T::SPAN_BYTES, 512, 1)
+                                                    : make_smem_desc_sw128(ring + T::A_BYTES, T::SPAN_BYTES, 1024));
+      constexpr uint64_t kStageStep = uint64_t(T::STAGE_BYTES >> 4);
+      uint64_t a_desc = a_desc0, b_desc = b_desc0;
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -372,14 +384,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int kb = 0; kb < kb_count; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * T::STAGE_BYTES);
-          const uint32_t sb = sa + T::A_BYTES;
-          const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
-          // An N-contiguous operand of 32-bit elements only exists in the "128-byte swizzle on
-          // 32-byte chunks" form: atoms of 128 bytes of N by 4 k-rows (512 bytes).
-          const uint64_t b_desc = B_NK ? make_smem_desc_sw128(sb, 16, 1024)
-                                  : (KIND == KIND_TF32 ? make_smem_desc(sb, T::SPAN_BYTES, 512, 1)
-                                                       : make_smem_desc_sw128(sb, T::SPAN_BYTES, 1024));
 #pragma unroll
           for (int j = 0; j < T::BK / T::UMMA_K; ++j) {
             // A (and a K-contiguous B) advance 32 bytes inside the swizzle row; an N-contiguous
@@ -393,7 +397,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           // the stage is free (in both CTAs of a pair) once these MMAs have read it
           if constexpr (CG == 2) umma_commit_pair(&empty_bar[stage], 3); else umma_commit(&empty_bar[stage]);
-          if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
+          a_desc += kStageStep;
+          b_desc += kStageStep;
+          if (++stage == T::STAGES) { stage = 0; phase ^= 1u; a_desc = a_desc0; b_desc = b_desc0; }
         }
         if (ok) {
           if constexpr (CG == 2) umma_commit_pair(&acc_full[ab], 3); else umma_commit(&acc_full[ab]);
