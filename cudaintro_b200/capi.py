@@ -243,8 +243,8 @@ def fill(t, seed: int, lo=None, hi=None):
 
 
 def set_tile_policy(cta_group: int = 0, tile_n: int = 0, group_rows: int = 0) -> None:
-    """Forces single CTAs (1) or CTA pairs (2), a tile width and the rows per tile-order group;
-    zeros restore the automatic choice."""
+    """Forces single CTAs (1), CTA pairs (2) or the K-split cluster kernel for skinny products (3), a tile
+    width and the rows per tile-order group; zeros restore the automatic choice."""
     _check(lib.b200_set_tile_policy(cta_group, tile_n, group_rows))
 
 
@@ -275,7 +275,8 @@ def set_store_policy(register_stores: bool = False) -> None:
 
 
 def set_split_k(splits: int = 0) -> None:
-    """0 or 1: K is not split (default); n: cut K into n ranges (single-CTA tensor-core kernels)."""
+    """0 or 1: whole tiles (default); n >= 2: opt-in split-K through a global workspace, every tile of a
+    product with fewer tiles than SMs, or the tiles of a last wave that is less than half full."""
     _check(lib.b200_set_split_k(splits))
 
 

@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted (it is not needed to *use* the fixtures):
 
-    make -C oracle ref REF=/root/reference
+    make -C oracle ref REF=<reference tree>
     python tests/golden/make_golden.py
 
 For every case the inputs come from a seeded numpy generator and the expected output from the
