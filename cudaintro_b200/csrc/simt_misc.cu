@@ -114,7 +114,7 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // rows); the first kRowCache float4 of every thread stay in registers, so rows of up to
 // 256 * 8 * 4 = 8192 elements are read from memory once.  4 B read, 1 B written per element.
 template <bool VEC>
-__global__ void __launch_bounds__(kQuantThreads)
+__global__ void __launch_bounds__(kQuantThreads, 4)
 quantize_rows_kernel(const float* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int64_t R,
                      int64_t C) {
   __shared__ float red[32];
