@@ -48,6 +48,15 @@ def test_gemm_result_layout_matches_reference_record(tmp_path):
     assert subprocess.run([str(exe)], capture_output=True, text=True).stdout.split() == ["32", "0", "8", "16", "24"]
 
 
+def test_public_header_is_plain_c(tmp_path):
+    """include/b200gemm.h is the binding surface for any host language: it must compile as C11 with
+    nothing but the standard headers it includes itself."""
+    src = tmp_path / "h.c"
+    src.write_text('#include "b200gemm.h"\nint main(void) { return (int)B200_OK; }\n')
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    "-fsyntax-only", str(src)], check=True)
+
+
 def test_bad_arguments_are_status_codes_not_crashes(cb):
     from cudaintro_b200 import capi
 
