@@ -308,10 +308,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const bool k_reversed = (it & 1) != 0;
         const int m0 = mb * TILE_M + int(cta_rank) * BM;
         const int n0 = nb * BN + int(cta_rank) * T::BN_CTA;
+        // (pass, kin) = (kbt / num_kb, kbt % num_kb), counted rather than divided: this lane's loop paces
+        // the CTA and an integer division per k-block is not free in it.
+        int pass = 0, kin = 0;
         for (int kbt = 0; kbt < kb_count; ++kbt) {
-          const int pass = X3 ? kbt / num_kb : 0;
-          const int kb = wi.nsplit > 1 ? kb_first + kbt
-                                      : (k_reversed ? num_kb - 1 - (kbt - pass * num_kb) : kbt - pass * num_kb);
+          const int kb = wi.nsplit > 1 ? kb_first + kbt : (k_reversed ? num_kb - 1 - kin : kin);
           const int a_row0 = (X3 && pass != 0) ? p.M : 0;                       // plane 1 = high parts
           const int b_row0 = (X3 && pass != 1) ? (B_NK ? p.N : p.K) : 0;
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -342,6 +343,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
+          if (++kin == num_kb) { kin = 0; ++pass; }
         }
       }
       if constexpr (CG == 2) {
