@@ -41,8 +41,10 @@ SIGNATURES = {
     "b200_linear": (_int, [_int, _p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _int, _p]),
     "b200_gemm_host": (_int, [_int, _p, _p, _p, _i64, _i64, _i64, _int]),
     "b200_host_release": (_int, []),
+    "b200_host_weights_upload": (_int, [_int, _p, _i64, _i64, C.POINTER(C.c_void_p)]),
+    "b200_gemm_host_weights": (_int, [_p, _p, _p, _i64]),
+    "b200_host_weights_free": (_int, [_p]),
     "b200_set_store_policy": (_int, [_int]),
-    "b200_set_split_k": (_int, [_int]),
     "b200_set_dependent_launch": (_int, [_int]),
     "b200_gemm_multi": (_int, [_int, _p, _p, C.POINTER(C.c_void_p), _int, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                _p]),
@@ -269,15 +271,30 @@ def gemm_host(dtype_code: int, a_np, b_np, c_np, M, N, K, layout=ROW_MAJOR) -> N
     _check(lib.b200_gemm_host(dtype_code, a_np.ctypes.data, b_np.ctypes.data, c_np.ctypes.data, M, N, K, layout))
 
 
+class HostWeights:
+    """A row-major [K, N] weight matrix uploaded once from host memory (numpy array or pinned torch CPU
+    tensor) to the current device; ``matmul(a, out)`` then multiplies host buffers against it."""
+
+    def __init__(self, dtype_code: int, b_host, K: int, N: int):
+        self._h = C.c_void_p()
+        ptr = b_host.ctypes.data if hasattr(b_host, "ctypes") else b_host.data_ptr()
+        _check(lib.b200_host_weights_upload(dtype_code, ptr, K, N, C.byref(self._h)))
+        self.K, self.N = K, N
+
+    def matmul(self, a_host, c_host, M: int) -> None:
+        pa = a_host.ctypes.data if hasattr(a_host, "ctypes") else a_host.data_ptr()
+        pc = c_host.ctypes.data if hasattr(c_host, "ctypes") else c_host.data_ptr()
+        _check(lib.b200_gemm_host_weights(self._h, pa, pc, M))
+
+    def close(self) -> None:
+        if self._h:
+            _check(lib.b200_host_weights_free(self._h))
+            self._h = C.c_void_p()
+
+
 def set_store_policy(register_stores: bool = False) -> None:
     """True: C is written straight from registers; False: automatic (staged TMA stores when aligned)."""
     _check(lib.b200_set_store_policy(1 if register_stores else 0))
-
-
-def set_split_k(splits: int = 0) -> None:
-    """0 or 1: whole tiles (default); n >= 2: opt-in split-K through a global workspace, every tile of a
-    product with fewer tiles than SMs, or the tiles of a last wave that is less than half full."""
-    _check(lib.b200_set_split_k(splits))
 
 
 def gemm_multi(what: int, a, b, dest_ptrs, M: int, N: int, K: int, row_scale=None, col_scale=None) -> None:

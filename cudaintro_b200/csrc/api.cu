@@ -69,10 +69,12 @@ int gemm_tensor(int kind, int epi, const void* A, const void* B, void* C, int64_
                           cs, 0, static_cast<cudaStream_t>(stream));
 }
 
-// Device workspace of the *_host entry point (one per process, grows on demand): the three
+// Device workspace of the *_host entry points, one per device (grows on demand): the three
 // matrices, one stream per direction of travel plus one for the kernels, and the events that chain
-// them chunk by chunk.
+// them chunk by chunk.  Calls on one device are serialised by the workspace's lock; calls on
+// different devices do not meet.
 constexpr int kHostChunks = 16;
+constexpr int kMaxDevices = 64;
 struct HostWorkspace {
   std::mutex mu;
   void* dA = nullptr;
@@ -85,17 +87,26 @@ struct HostWorkspace {
   cudaEvent_t whole_in = nullptr;     // the operand that is needed whole has arrived
   cudaEvent_t chunk_in[kHostChunks] = {nullptr};
   cudaEvent_t chunk_done[kHostChunks] = {nullptr};
-} g_ws;
+} g_ws[kMaxDevices];
 
-int host_streams_ready() {
-  if (g_ws.stream) return B200_OK;
-  B200_CUDA_TRY(cudaStreamCreateWithFlags(&g_ws.stream, cudaStreamNonBlocking));
-  B200_CUDA_TRY(cudaStreamCreateWithFlags(&g_ws.in_stream, cudaStreamNonBlocking));
-  B200_CUDA_TRY(cudaStreamCreateWithFlags(&g_ws.out_stream, cudaStreamNonBlocking));
-  B200_CUDA_TRY(cudaEventCreateWithFlags(&g_ws.whole_in, cudaEventDisableTiming));
+int current_workspace(HostWorkspace** out) {
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(B200_ERR_UNSUPPORTED, "device ordinal %d is beyond the host-workspace table", dev);
+  *out = &g_ws[dev];
+  return B200_OK;
+}
+
+int host_streams_ready(HostWorkspace& ws) {
+  if (ws.stream) return B200_OK;
+  B200_CUDA_TRY(cudaStreamCreateWithFlags(&ws.stream, cudaStreamNonBlocking));
+  B200_CUDA_TRY(cudaStreamCreateWithFlags(&ws.in_stream, cudaStreamNonBlocking));
+  B200_CUDA_TRY(cudaStreamCreateWithFlags(&ws.out_stream, cudaStreamNonBlocking));
+  B200_CUDA_TRY(cudaEventCreateWithFlags(&ws.whole_in, cudaEventDisableTiming));
   for (int i = 0; i < kHostChunks; ++i) {
-    B200_CUDA_TRY(cudaEventCreateWithFlags(&g_ws.chunk_in[i], cudaEventDisableTiming));
-    B200_CUDA_TRY(cudaEventCreateWithFlags(&g_ws.chunk_done[i], cudaEventDisableTiming));
+    B200_CUDA_TRY(cudaEventCreateWithFlags(&ws.chunk_in[i], cudaEventDisableTiming));
+    B200_CUDA_TRY(cudaEventCreateWithFlags(&ws.chunk_done[i], cudaEventDisableTiming));
   }
   return B200_OK;
 }
@@ -108,6 +119,92 @@ int grow(void** p, size_t* cap, size_t need) {
   B200_CUDA_TRY(cudaMalloc(p, need));
   *cap = need;
   return B200_OK;
+}
+
+bool host_dtype_sizes(int dtype, size_t* in_elem, size_t* out_elem) {
+  switch (dtype) {
+    case B200_I8: *in_elem = 1; *out_elem = 4; return true;
+    case B200_F16: case B200_BF16: *in_elem = 2; *out_elem = 2; return true;
+    case B200_F32: *in_elem = 4; *out_elem = 4; return true;
+  }
+  return false;
+}
+
+// A weight matrix kept on the device between host-buffer calls (b200_host_weights_*).
+struct HostWeights {
+  uint32_t magic;
+  int device;
+  int dtype;
+  int64_t K, N;
+  void* dB;
+};
+constexpr uint32_t kWeightsMagic = 0xb2005eedu;
+
+}  // namespace
+
+int dispatch_gemm(int what, const void* A, const void* B, void* C, const float* rs, const float* cs, int64_t M,
+                  int64_t N, int64_t K, int layout, int f32_mode, void* stream);
+
+namespace {
+
+// The slab pipeline shared by the host-buffer entry points.  `whole_dev` is the operand every line
+// of the output needs, already on the device (or on its way: the kernel stream waits for
+// `whole_ready` when that is not null).  The other operand travels in up to 16 slabs of `units`
+// lines (rows of A; columns of B for the column-major layout); slab i + 1 is on its way up while
+// slab i is multiplied and slab i - 1 of the result is on its way down.  Whatever happens, every
+// copy and kernel issued here has finished before the function returns: the caller's buffers are
+// never touched after an error return.
+int run_host_slabs(HostWorkspace& ws, int dtype, int layout, const void* whole_dev, cudaEvent_t whole_ready,
+                   const char* slab_src, char* slab_dst, char* c_dev_base, char* c_host, int64_t M, int64_t N,
+                   int64_t K, size_t in_elem, size_t out_elem) {
+  const bool col = layout == B200_COL_MAJOR_NN;
+  const int64_t units = col ? N : M;                       // rows of A / columns of B
+  const size_t in_unit = size_t(K) * in_elem;              // bytes of one of them
+  const size_t out_unit = size_t(col ? M : N) * out_elem;  // bytes of the matching line of C
+  // Slabs of a multiple of 256 units (the tallest tile), at least 512, at most 16 of them.
+  int64_t per = (units + kHostChunks - 1) / kHostChunks;
+  per = (per + 255) / 256 * 256;
+  if (per < 512) per = 512;
+
+  int rc = B200_OK;
+  cudaError_t ce = cudaSuccess;
+  const char* what = "";
+#define HOST_STEP(call)                         \
+  if (rc == B200_OK && ce == cudaSuccess) {     \
+    ce = (call);                                \
+    if (ce != cudaSuccess) what = #call;        \
+  }
+  if (whole_ready) HOST_STEP(cudaStreamWaitEvent(ws.stream, whole_ready, 0));
+  int i = 0;
+  for (int64_t u0 = 0; u0 < units && rc == B200_OK && ce == cudaSuccess; u0 += per, ++i) {
+    const int64_t n_units = units - u0 < per ? units - u0 : per;
+    HOST_STEP(cudaMemcpyAsync(slab_dst + u0 * in_unit, slab_src + u0 * in_unit, size_t(n_units) * in_unit,
+                              cudaMemcpyHostToDevice, ws.in_stream));
+    HOST_STEP(cudaEventRecord(ws.chunk_in[i], ws.in_stream));
+    HOST_STEP(cudaStreamWaitEvent(ws.stream, ws.chunk_in[i], 0));
+    if (rc != B200_OK || ce != cudaSuccess) break;
+    char* c_dev = c_dev_base + u0 * out_unit;
+    if (col)
+      rc = dispatch_gemm(dtype, whole_dev, slab_dst + u0 * in_unit, c_dev, nullptr, nullptr, M, n_units, K, layout,
+                         B200_F32_FFMA, ws.stream);
+    else
+      rc = dispatch_gemm(dtype, slab_dst + u0 * in_unit, whole_dev, c_dev, nullptr, nullptr, n_units, N, K, layout,
+                         B200_F32_FFMA, ws.stream);
+    HOST_STEP(cudaEventRecord(ws.chunk_done[i], ws.stream));
+    HOST_STEP(cudaStreamWaitEvent(ws.out_stream, ws.chunk_done[i], 0));
+    HOST_STEP(cudaMemcpyAsync(c_host + u0 * out_unit, c_dev, size_t(n_units) * out_unit, cudaMemcpyDeviceToHost,
+                              ws.out_stream));
+  }
+#undef HOST_STEP
+  // Common tail, reached on success and on every failure alike: wait for all three streams.
+  const cudaError_t e_in = cudaStreamSynchronize(ws.in_stream);
+  const cudaError_t e_out = cudaStreamSynchronize(ws.out_stream);
+  const int dev_rc = b200_check_device(ws.stream);  // synchronises the kernel stream
+  if (rc) return rc;
+  if (ce != cudaSuccess) return fail(B200_ERR_CUDA, "%s: %s", what, cudaGetErrorString(ce));
+  if (e_in != cudaSuccess) return fail(B200_ERR_CUDA, "host-to-device copies: %s", cudaGetErrorString(e_in));
+  if (e_out != cudaSuccess) return fail(B200_ERR_CUDA, "device-to-host copies: %s", cudaGetErrorString(e_out));
+  return dev_rc;
 }
 
 }  // namespace
@@ -222,8 +319,8 @@ extern "C" int b200_gemm_naive(int dtype, const void* A, const void* B, void* C,
   return launch_naive(dtype, A, B, C, M, N, K, lda, ldb, ldc, layout, static_cast<cudaStream_t>(stream));
 }
 
-static int dispatch(int what, const void* A, const void* B, void* C, const float* rs, const float* cs, int64_t M,
-                    int64_t N, int64_t K, int layout, int f32_mode, void* stream) {
+int b200::dispatch_gemm(int what, const void* A, const void* B, void* C, const float* rs, const float* cs, int64_t M,
+                        int64_t N, int64_t K, int layout, int f32_mode, void* stream) {
   switch (what) {
     case B200_I8:
       return b200_gemm_i8_i32(static_cast<const int8_t*>(A), static_cast<const int8_t*>(B),
@@ -252,7 +349,7 @@ extern "C" int b200_time_gemm(int what, const void* A, const void* B, void* C, c
   int rc = B200_OK;
   cudaEventRecord(e0, stream);
   for (int i = 0; i < iters && rc == B200_OK; ++i)
-    rc = dispatch(what, A, B, C, row_scale, col_scale, M, N, K, layout, f32_mode, stream_);
+    rc = dispatch_gemm(what, A, B, C, row_scale, col_scale, M, N, K, layout, f32_mode, stream_);
   cudaEventRecord(e1, stream);
   cudaError_t se = cudaEventSynchronize(e1);
   if (rc == B200_OK && se != cudaSuccess) rc = fail(B200_ERR_CUDA, "cudaEventSynchronize: %s", cudaGetErrorString(se));
@@ -278,92 +375,123 @@ extern "C" int b200_gemm_host(int dtype, const void* A, const void* B, void* C, 
   if (layout != B200_ROW_MAJOR && layout != B200_COL_MAJOR_NN && layout != B200_ROW_MAJOR_BT)
     return fail(B200_ERR_BAD_ARGUMENT, "unknown layout %d", layout);
   size_t in_elem, out_elem;
-  switch (dtype) {
-    case B200_I8: in_elem = 1; out_elem = 4; break;
-    case B200_F16: case B200_BF16: in_elem = 2; out_elem = 2; break;
-    case B200_F32: in_elem = 4; out_elem = 4; break;
-    default: return fail(B200_ERR_BAD_ARGUMENT, "unknown dtype %d", dtype);
-  }
-  std::lock_guard<std::mutex> lock(g_ws.mu);
-  int rc = host_streams_ready();
+  if (!host_dtype_sizes(dtype, &in_elem, &out_elem)) return fail(B200_ERR_BAD_ARGUMENT, "unknown dtype %d", dtype);
+  HostWorkspace* wsp = nullptr;
+  int rc = current_workspace(&wsp);
   if (rc) return rc;
+  HostWorkspace& ws = *wsp;
+  std::lock_guard<std::mutex> lock(ws.mu);
+  if ((rc = host_streams_ready(ws))) return rc;
   const size_t bytesA = size_t(M) * K * in_elem, bytesB = size_t(K) * N * in_elem, bytesC = size_t(M) * N * out_elem;
-  if ((rc = grow(&g_ws.dA, &g_ws.capA, bytesA))) return rc;
-  if ((rc = grow(&g_ws.dB, &g_ws.capB, bytesB))) return rc;
-  if ((rc = grow(&g_ws.dC, &g_ws.capC, bytesC))) return rc;
+  if ((rc = grow(&ws.dA, &ws.capA, bytesA))) return rc;
+  if ((rc = grow(&ws.dB, &ws.capB, bytesB))) return rc;
+  if ((rc = grow(&ws.dC, &ws.capC, bytesC))) return rc;
 
   const bool col = layout == B200_COL_MAJOR_NN;
   const char* whole_src = static_cast<const char*>(col ? A : B);
-  char* whole_dst = static_cast<char*>(col ? g_ws.dA : g_ws.dB);
+  char* whole_dst = static_cast<char*>(col ? ws.dA : ws.dB);
   const size_t whole_bytes = col ? bytesA : bytesB;
-  const char* slab_src = static_cast<const char*>(col ? B : A);
-  char* slab_dst = static_cast<char*>(col ? g_ws.dB : g_ws.dA);
-  const int64_t units = col ? N : M;                                 // rows of A / columns of B
-  const size_t in_unit = size_t(K) * in_elem;                        // bytes of one of them
-  const size_t out_unit = size_t(col ? M : N) * out_elem;            // bytes of the matching line of C
-  // Slabs of a multiple of 256 units (the tallest tile), at least 512, at most 16 of them.
-  int64_t per = (units + kHostChunks - 1) / kHostChunks;
-  per = (per + 255) / 256 * 256;
-  if (per < 512) per = 512;
-
-  B200_CUDA_TRY(cudaMemcpyAsync(whole_dst, whole_src, whole_bytes, cudaMemcpyHostToDevice, g_ws.in_stream));
-  B200_CUDA_TRY(cudaEventRecord(g_ws.whole_in, g_ws.in_stream));
-  B200_CUDA_TRY(cudaStreamWaitEvent(g_ws.stream, g_ws.whole_in, 0));
-  int i = 0;
-  for (int64_t u0 = 0; u0 < units; u0 += per, ++i) {
-    const int64_t n_units = units - u0 < per ? units - u0 : per;
-    B200_CUDA_TRY(cudaMemcpyAsync(slab_dst + u0 * in_unit, slab_src + u0 * in_unit, size_t(n_units) * in_unit,
-                                  cudaMemcpyHostToDevice, g_ws.in_stream));
-    B200_CUDA_TRY(cudaEventRecord(g_ws.chunk_in[i], g_ws.in_stream));
-    B200_CUDA_TRY(cudaStreamWaitEvent(g_ws.stream, g_ws.chunk_in[i], 0));
-    char* c_dev = static_cast<char*>(g_ws.dC) + u0 * out_unit;
-    if (col)
-      rc = dispatch(dtype, g_ws.dA, slab_dst + u0 * in_unit, c_dev, nullptr, nullptr, M, n_units, K, layout,
-                    B200_F32_FFMA, g_ws.stream);
-    else
-      rc = dispatch(dtype, slab_dst + u0 * in_unit, g_ws.dB, c_dev, nullptr, nullptr, n_units, N, K, layout,
-                    B200_F32_FFMA, g_ws.stream);
-    if (rc) break;
-    B200_CUDA_TRY(cudaEventRecord(g_ws.chunk_done[i], g_ws.stream));
-    B200_CUDA_TRY(cudaStreamWaitEvent(g_ws.out_stream, g_ws.chunk_done[i], 0));
-    B200_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(C) + u0 * out_unit, c_dev, size_t(n_units) * out_unit,
-                                  cudaMemcpyDeviceToHost, g_ws.out_stream));
+  // Nothing else is in flight yet, so a failure of these two calls may return at once.
+  B200_CUDA_TRY(cudaMemcpyAsync(whole_dst, whole_src, whole_bytes, cudaMemcpyHostToDevice, ws.in_stream));
+  cudaError_t ev = cudaEventRecord(ws.whole_in, ws.in_stream);
+  if (ev != cudaSuccess) {
+    cudaStreamSynchronize(ws.in_stream);
+    return fail(B200_ERR_CUDA, "cudaEventRecord: %s", cudaGetErrorString(ev));
   }
-  // Everything issued must have finished before the buffers are reused or an error is returned.
-  cudaError_t e_in = cudaStreamSynchronize(g_ws.in_stream);
-  cudaError_t e_out = cudaStreamSynchronize(g_ws.out_stream);
-  const int dev_rc = b200_check_device(g_ws.stream);
-  if (rc) return rc;
-  if (e_in != cudaSuccess) return fail(B200_ERR_CUDA, "host-to-device copies: %s", cudaGetErrorString(e_in));
-  if (e_out != cudaSuccess) return fail(B200_ERR_CUDA, "device-to-host copies: %s", cudaGetErrorString(e_out));
-  return dev_rc;
+  return run_host_slabs(ws, dtype, layout, whole_dst, ws.whole_in, static_cast<const char*>(col ? B : A),
+                        static_cast<char*>(col ? ws.dB : ws.dA), static_cast<char*>(ws.dC), static_cast<char*>(C),
+                        M, N, K, in_elem, out_elem);
 }
 
+// Frees the host-buffer workspace of the CURRENT device (weights uploaded with
+// b200_host_weights_upload are separate objects and stay).
 extern "C" int b200_host_release(void) {
-  std::lock_guard<std::mutex> lock(g_ws.mu);
-  if (g_ws.dA) cudaFree(g_ws.dA);
-  if (g_ws.dB) cudaFree(g_ws.dB);
-  if (g_ws.dC) cudaFree(g_ws.dC);
-  g_ws.dA = g_ws.dB = g_ws.dC = nullptr;
-  g_ws.capA = g_ws.capB = g_ws.capC = 0;
-  if (g_ws.stream) {
-    cudaStreamDestroy(g_ws.stream);
-    cudaStreamDestroy(g_ws.in_stream);
-    cudaStreamDestroy(g_ws.out_stream);
-    cudaEventDestroy(g_ws.whole_in);
+  HostWorkspace* wsp = nullptr;
+  int rc = current_workspace(&wsp);
+  if (rc) return rc;
+  HostWorkspace& ws = *wsp;
+  std::lock_guard<std::mutex> lock(ws.mu);
+  if (ws.dA) cudaFree(ws.dA);
+  if (ws.dB) cudaFree(ws.dB);
+  if (ws.dC) cudaFree(ws.dC);
+  ws.dA = ws.dB = ws.dC = nullptr;
+  ws.capA = ws.capB = ws.capC = 0;
+  if (ws.stream) {
+    cudaStreamDestroy(ws.stream);
+    cudaStreamDestroy(ws.in_stream);
+    cudaStreamDestroy(ws.out_stream);
+    cudaEventDestroy(ws.whole_in);
     for (int i = 0; i < kHostChunks; ++i) {
-      cudaEventDestroy(g_ws.chunk_in[i]);
-      cudaEventDestroy(g_ws.chunk_done[i]);
+      cudaEventDestroy(ws.chunk_in[i]);
+      cudaEventDestroy(ws.chunk_done[i]);
     }
   }
-  g_ws.stream = g_ws.in_stream = g_ws.out_stream = nullptr;
+  ws.stream = ws.in_stream = ws.out_stream = nullptr;
   return B200_OK;
+}
+
+// ------------------------------------------------------------------ host buffers, weights kept on the device
+
+extern "C" int b200_host_weights_upload(int dtype, const void* B, int64_t K, int64_t N, void** weights) {
+  if (!B || !weights) return fail(B200_ERR_BAD_ARGUMENT, "null pointer");
+  if (K <= 0 || N <= 0) return fail(B200_ERR_BAD_ARGUMENT, "K and N must be positive");
+  size_t in_elem, out_elem;
+  if (!host_dtype_sizes(dtype, &in_elem, &out_elem)) return fail(B200_ERR_BAD_ARGUMENT, "unknown dtype %d", dtype);
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  void* dB = nullptr;
+  B200_CUDA_TRY(cudaMalloc(&dB, size_t(K) * N * in_elem));
+  cudaError_t e = cudaMemcpy(dB, B, size_t(K) * N * in_elem, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    cudaFree(dB);
+    return fail(B200_ERR_CUDA, "upload of the weights: %s", cudaGetErrorString(e));
+  }
+  *weights = new HostWeights{kWeightsMagic, dev, dtype, K, N, dB};
+  return B200_OK;
+}
+
+extern "C" int b200_host_weights_free(void* weights) {
+  if (!weights) return B200_OK;
+  HostWeights* w = static_cast<HostWeights*>(weights);
+  if (w->magic != kWeightsMagic) return fail(B200_ERR_BAD_ARGUMENT, "not a weights handle");
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev != w->device) B200_CUDA_TRY(cudaSetDevice(w->device));
+  cudaError_t e = cudaFree(w->dB);
+  if (dev != w->device) cudaSetDevice(dev);
+  w->magic = 0;
+  delete w;
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFree(weights): %s", cudaGetErrorString(e));
+  return B200_OK;
+}
+
+extern "C" int b200_gemm_host_weights(const void* weights, const void* A, void* C, int64_t M) {
+  if (!weights || !A || !C) return fail(B200_ERR_BAD_ARGUMENT, "null pointer");
+  const HostWeights* w = static_cast<const HostWeights*>(weights);
+  if (w->magic != kWeightsMagic) return fail(B200_ERR_BAD_ARGUMENT, "not a weights handle");
+  if (M <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M must be positive");
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev != w->device)
+    return fail(B200_ERR_UNSUPPORTED, "the weights live on device %d but device %d is current", w->device, dev);
+  size_t in_elem = 0, out_elem = 0;
+  host_dtype_sizes(w->dtype, &in_elem, &out_elem);
+  HostWorkspace* wsp = nullptr;
+  int rc = current_workspace(&wsp);
+  if (rc) return rc;
+  HostWorkspace& ws = *wsp;
+  std::lock_guard<std::mutex> lock(ws.mu);
+  if ((rc = host_streams_ready(ws))) return rc;
+  if ((rc = grow(&ws.dA, &ws.capA, size_t(M) * w->K * in_elem))) return rc;
+  if ((rc = grow(&ws.dC, &ws.capC, size_t(M) * w->N * out_elem))) return rc;
+  return run_host_slabs(ws, w->dtype, B200_ROW_MAJOR, w->dB, nullptr, static_cast<const char*>(A),
+                        static_cast<char*>(ws.dA), static_cast<char*>(ws.dC), static_cast<char*>(C), M, w->N, w->K,
+                        in_elem, out_elem);
 }
 
 // ------------------------------------------------------------------ several destinations, peer memory
 
 extern "C" int b200_set_store_policy(int register_stores) { return set_store_policy(register_stores); }
-extern "C" int b200_set_split_k(int splits) { return set_split_k(splits); }
 extern "C" int b200_set_dependent_launch(int enabled) { return set_dependent_launch(enabled); }
 
 extern "C" int b200_gemm_multi(int what, const void* A, const void* B, void* const* C_list, int n_dest,

@@ -27,9 +27,6 @@
 // with K contiguous.  The first form is fed to the tensor cores as an "MN-major" operand: the
 // tile is loaded as column spans of 128 bytes, each BK rows tall.
 //
-// Optional split-K: a work item is (tile, K range); partial accumulators meet in a workspace and
-// the item that finishes a tile last adds them up in range order.
-//
 // Every mbarrier wait is bounded; a wait that runs out raises a CTA-wide abort flag, all roles
 // drain, tensor memory is freed, and a status word tells the host that the result is invalid.
 #include <cuda.h>
@@ -94,17 +91,6 @@ struct GemmArgs {
   int tiles_m, tiles_n;
   int group_m;  // m-tiles per group of the tile order
   int store_mode;  // StoreMode: how the epilogue writes C
-  // Work items.  Items [0, full_items) are whole tiles; every later tile is cut along K into `splits`
-  // ranges of `kb_per_split` k-blocks, one item each (full_items = 0: every tile is cut; splits = 1:
-  // none is).  Cutting the tiles of a partly filled last wave lets the idle SMs take half of each.
-  // Split-K: K is cut into `splits` ranges of `kb_per_split` k-blocks, one work
-  // item each; partial accumulators go to `ws` ([tile][split][128][BN] 32-bit words) and the item that
-  // finishes a tile last (per `counters[tile]`, zero on entry, reset on exit) adds them up and stores C.
-  int splits;
-  int kb_per_split;
-  int full_items;
-  uint32_t* ws;
-  uint32_t* counters;
   int single_pass;  // tf32 kind only: 1 = plain fp32 operands, one pass (no split planes)
   const float* row_scale;
   const float* col_scale;
@@ -126,19 +112,6 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   int r = t - g * per_group;
   mb = first_m + r % gm;
   nb = r / gm;
-}
-
-struct WorkItem {
-  int tile;    // index in the tile order
-  int split;   // which K range of the tile (0 for a whole tile)
-  int nsplit;  // 1 = whole tile
-  int local;   // index among the cut tiles (workspace and counter slot)
-};
-__device__ __forceinline__ WorkItem decode_item(const GemmArgs& p, int t) {
-  if (t < p.full_items) return WorkItem{t, 0, 1, 0};
-  const int u = t - p.full_items;
-  const int local = u / p.splits;
-  return WorkItem{p.full_items + local, u - local * p.splits, p.splits, local};
 }
 
 // Converts W accumulator columns of one row into output words: W words for 4-byte outputs,
@@ -239,14 +212,16 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint64_t* acc_empty = acc_full + 2;          // [2] epilogue -> MMA           (pair: the leader's is used)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  volatile uint32_t* epi_go = tmem_slot + 2;  // epilogue warps: "this tile's accumulator arrived"
+  // Epilogue warps: "this tile's accumulator arrived".  Two words used in turn, so that the warp that
+  // posts the word for tile i + 1 never overwrites the one a slower warp is still reading for tile i.
+  volatile uint32_t* epi_go_pair = tmem_slot + 2;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t cta_rank = CG == 2 ? cluster_cta_rank() : 0u;  // 0 = leader of the pair
   const int first_tile = CG == 2 ? int(blockIdx.x >> 1) : int(blockIdx.x);
   const int tile_step = CG == 2 ? int(gridDim.x >> 1) : int(gridDim.x);
-  const int num_tiles = p.full_items + (p.tiles_m * p.tiles_n - p.full_items) * p.splits;  // work items
+  const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_kb = (p.K + T::BK - 1) / T::BK;
   // Split-operand fp32 (3xTF32): A and B each arrive as two stacked planes, low parts on top of
   // high parts, and K is walked three times: lo*hi, then hi*lo, then hi*hi (small terms first).
@@ -298,10 +273,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int it = 0;
       for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
         int mb, nb;
-        const WorkItem wi = decode_item(p, t);
-        tile_coords(wi.tile, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
-        const int kb_first = wi.split * p.kb_per_split;
-        const int kb_count = wi.nsplit == 1 ? total_kb : min(p.kb_per_split, num_kb - kb_first);
+        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
         // Every other tile walks K backwards: a tile then starts on the k-blocks its predecessor
         // touched last, which are the ones still in L2 (a forward-only sweep over a slab larger
         // than the cache would evict each block just before it is needed again).
@@ -311,8 +283,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // (pass, kin) = (kbt / num_kb, kbt % num_kb), counted rather than divided: this lane's loop paces
         // the CTA and an integer division per k-block is not free in it.
         int pass = 0, kin = 0;
-        for (int kbt = 0; kbt < kb_count; ++kbt) {
-          const int kb = wi.nsplit > 1 ? kb_first + kbt : (k_reversed ? num_kb - 1 - kin : kin);
+        for (int kbt = 0; kbt < total_kb; ++kbt) {
+          const int kb = k_reversed ? num_kb - 1 - kin : kin;
           const int a_row0 = (X3 && pass != 0) ? p.M : 0;                       // plane 1 = high parts
           const int b_row0 = (X3 && pass != 1) ? (B_NK ? p.N : p.K) : 0;
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -381,9 +353,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!mbar_wait_bounded(&acc_empty[ab], acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);
-        const WorkItem wi = decode_item(p, t);
-        const int kb_count = wi.nsplit == 1 ? total_kb : min(p.kb_per_split, num_kb - wi.split * p.kb_per_split);
-        for (int kb = 0; kb < kb_count; ++kb) {
+        for (int kb = 0; kb < total_kb; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
 #pragma unroll
@@ -422,10 +392,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int it = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mb, nb;
-      const WorkItem wi = decode_item(p, t);
-      tile_coords(wi.tile, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+      tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
       const int ab = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      volatile uint32_t* epi_go = epi_go_pair + ab;
       // One warp polls the barrier; all four then agree on the outcome, so that they always meet at
       // the same hardware barriers below even when the wait had to be given up.
       if (warp == 2) {
@@ -440,24 +410,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       float rs = 0.f;
       if constexpr (EPI == EPI_W8A8_BF16) rs = row < p.M ? __ldg(p.row_scale + row) : 0.f;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(ab * BN);
-      if (wi.nsplit > 1) {
-        // A K range of a cut tile: park the raw accumulator in the workspace; whoever completes the
-        // tile adds the ranges up in range order (so the result does not depend on who came last).
-        uint32_t* part =
-            p.ws + (((size_t(wi.local) * p.splits + wi.split) * CG + cta_rank) * BM + r_in_tile) * BN;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          if (nb * BN + c * 32 >= p.N) break;
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + uint32_t(c * 32), v);
-          tmem_ld_wait();
-          if (row < p.M) {
-            uint4* dst = reinterpret_cast<uint4*>(part + c * 32);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          }
-        }
-      } else if (p.store_mode == STORE_TMA) {
+      if (p.store_mode == STORE_TMA) {
         // Stage 128 x 128-byte output tiles in shared memory (swizzled like the tensor map expects)
         // and let TMA write them: whole rows per request, clipped at the edges of C, one request
         // per destination buffer.
@@ -513,49 +466,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (lane == 0) {
         if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[ab]), 0));
         else mbar_arrive(&acc_empty[ab]);
-      }
-      if (wi.nsplit > 1) {
-        __threadfence();  // this thread's partial row is visible device-wide before the count goes up
-        named_barrier_sync(1, kEpiThreads);
-        if (store_thread) {
-          uint32_t* counter = p.counters + wi.local * CG + cta_rank;
-          const uint32_t done = atomicAdd(counter, 1u);
-          const bool last = done == uint32_t(p.splits - 1);
-          if (last) *counter = 0;  // ready for the next launch
-          *epi_go = last ? 1u : 0u;
-        }
-        named_barrier_sync(1, kEpiThreads);
-        if (*epi_go != 0u) {
-          // All 128 threads share the tile: a unit is 8 consecutive columns of one row, consecutive
-          // threads take consecutive units, so reads of the partial sums and stores to C are coalesced
-          // and every thread has all its loads in flight at once.
-          __threadfence();
-          const int valid_rows = min(BM, p.M - tile_row0);
-          const uint32_t* base = p.ws + (size_t(wi.local) * p.splits * CG + cta_rank) * BM * BN;
-          for (int u = r_in_tile; u < valid_rows * (BN / 8); u += kEpiThreads) {
-            const int ur = u / (BN / 8), uc = (u - ur * (BN / 8)) * 8;
-            const int n0 = nb * BN + uc;
-            if (n0 >= p.N) continue;
-            uint32_t v[8], w[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = 0u;
-            for (int sp = 0; sp < p.splits; ++sp) {
-              const uint4* src = reinterpret_cast<const uint4*>(base + (size_t(sp) * CG * BM + ur) * BN + uc);
-              const uint4 u0 = __ldcg(src), u1 = __ldcg(src + 1);
-              const uint32_t in[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                if constexpr (KIND == KIND_I8) v[i] += in[i];
-                else v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(in[i]));
-              }
-            }
-            float urs = 0.f;
-            if constexpr (EPI == EPI_W8A8_BF16) urs = __ldg(p.row_scale + tile_row0 + ur);
-            pack_chunk<EPI, 8>(p, n0, v, urs, w);
-            store_chunk<EPI, 8>(p, tile_row0 + ur, n0, w);
-          }
-        }
-        named_barrier_sync(1, kEpiThreads);  // epi_go is rewritten by the next item
       }
     }
     if (store_thread) tma_store_wait_all<0>();  // every output tile has left for global memory
@@ -689,7 +599,7 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
   int sms = 0;
   rc = sm_count_of_current_device(&sms);
   if (rc) return rc;
-  int tiles = args.full_items + (args.tiles_m * args.tiles_n - args.full_items) * args.splits;  // work items
+  const int tiles = args.tiles_m * args.tiles_n;
   // Launch with programmatic stream serialisation: this grid's CTAs may be scheduled, and run their
   // set-up (barrier init, TMEM allocation, descriptor prefetch), while the kernel before it in the
   // stream is still draining; they touch no global data before griddepcontrol.wait, which holds them
@@ -738,37 +648,14 @@ int launch_major(bool b_nk, const void* A, const void* B, const GemmArgs& args, 
 
 int g_force_cg = 0, g_force_bn = 0, g_group_rows = 0;  // 0 = automatic; set through b200_set_tile_policy
 int g_force_store = 0;                                  // 0 = automatic, STORE_VECTOR = register stores
-int g_force_splits = 0;                                 // 0 = automatic, 1 = never split K, n = n ranges
 thread_local bool g_tf32_single_pass_call = false;      // set by launch_sgemm_tf32 around its launch
 
-// Per-tile counters of the cut tiles: a persistent array per device, zeroed once; every launch takes
-// the next of 64 slots (launches in flight at the same time therefore use different counters) and
-// leaves its counters at zero again, because the item that completes a tile resets its counter.
-constexpr int kCounterSlotWords = 1024;
-constexpr int kCounterSlots = 64;
-int split_k_counters(uint32_t** out) {
-  static std::mutex mu;
-  static uint32_t* base[64] = {nullptr};
-  static unsigned next_slot = 0;
-  int dev = 0;
-  B200_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(B200_ERR_UNSUPPORTED, "device ordinal %d is beyond the counter table", dev);
-  std::lock_guard<std::mutex> lock(mu);
-  if (!base[dev]) {
-    void* p = nullptr;
-    const size_t bytes = size_t(kCounterSlots) * kCounterSlotWords * sizeof(uint32_t);
-    B200_CUDA_TRY(cudaMalloc(&p, bytes));
-    B200_CUDA_TRY(cudaMemset(p, 0, bytes));
-    base[dev] = static_cast<uint32_t*>(p);
-  }
-  *out = base[dev] + size_t(next_slot++ % kCounterSlots) * kCounterSlotWords;
-  return B200_OK;
-}
-
-// Stream-ordered memory pool of the split-K workspaces, one per device.  It keeps what it has
-// handed out before (release threshold at the maximum), so that after the first call an
-// allocation is a host-side bookkeeping step and never reaches the driver's allocator.
-int split_k_pool(cudaMemPool_t* out) {
+// Stream-ordered memory pool for per-call scratch (the split planes of the 3xTF32 product), one per
+// device.  It keeps what it has handed out before (release threshold at the maximum), so that after
+// the first call an allocation is a host-side bookkeeping step and never reaches the driver's
+// allocator; an allocation and its release are ordered on the caller's stream, so calls on
+// different streams never share scratch.
+int scratch_pool(cudaMemPool_t* out) {
   static std::mutex mu;
   static cudaMemPool_t pools[64] = {nullptr};
   int dev = 0;
@@ -837,12 +724,6 @@ int set_tile_policy(int cg, int bn, int group_rows) {
   g_force_cg = cg;
   g_force_bn = bn;
   g_group_rows = group_rows;
-  return B200_OK;
-}
-
-int set_split_k(int splits) {
-  if (splits < 0 || splits > 64) return fail(B200_ERR_BAD_ARGUMENT, "split-K: between 0 (automatic) and 64 ranges");
-  g_force_splits = splits;
   return B200_OK;
 }
 
@@ -963,8 +844,7 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   // lets every SM pull clearly less through its TMA unit than the tiles chosen above would (columns
   // of B per k-block, plus the 128 rows of A at the 0.3 they were measured to weigh, coming from L2),
   // that kernel takes it.
-  const bool nothing_forced = force_bn == 0 && g_force_bn == 0 && g_force_cg == 0 && g_force_splits == 0 &&
-                              g_force_store == 0;
+  const bool nothing_forced = force_bn == 0 && g_force_bn == 0 && g_force_cg == 0 && g_force_store == 0;
   if (skinny_kind && n_dest == 1 && (skinny_forced || (nothing_forced && M <= BM))) {
     const int64_t k_blocks = (K * elem + 127) / 128;
     const int64_t tiles = int64_t(args.tiles_m) * ((N + bn - 1) / bn);
@@ -975,70 +855,7 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
     if (rc || used) return rc;
   }
 
-  // Work items: whole tiles, then (on request only, b200_set_split_k(n >= 2)) tiles cut along K:
-  //  * a product with more tiles than SMs (or SM pairs) whose last wave is less than half full gets
-  //    the tiles of that wave cut into up to n ranges, so that the idle SMs share them;
-  //  * a product with fewer tiles than SMs (single CTAs) gets every tile cut into n ranges.
-  // Partial sums meet in a stream-ordered workspace; the per-tile counters live in a persistent,
-  // self-resetting array (one slot per launch in flight).
-  // Neither pays with the present exchange of partial sums (row-per-thread stores of the raw
-  // accumulator, a fence, a counter, a second pass by the last arriver: about 10 us per cut item).
-  // Measured: int8 4096^3 56 -> 77 us and the fp16 linear layer M = 1024 77 -> 100 us with the last
-  // wave cut; M = 16 / 128 linear layers 31 / 33 us uncut against 29 / 64 us with every tile cut in 3.
-  args.splits = 1;
-  args.kb_per_split = 0;
-  args.ws = nullptr;
-  args.counters = nullptr;
-  void* split_ws = nullptr;
-  {
-    const int bk = 128 / elem;
-    const int64_t num_kb = (K + bk - 1) / bk;
-    const int64_t workers = cg == 2 ? sms / 2 : sms;
-    int64_t total = ((M + BM * cg - 1) / (BM * cg)) * ((N + bn - 1) / bn);
-    int64_t full = total, want = 1;
-    const bool asked = kind != KIND_TF32 && g_force_splits > 1 && n_dest == 1;
-    if (asked && total > workers) {
-      const int64_t tail = total % workers;
-      if (tail > 0 && 2 * tail <= workers) {
-        want = workers / tail;
-        if (want > g_force_splits) want = g_force_splits;
-        if (want >= 2) full = total - tail;
-      }
-    } else if (asked && cg == 1 && force_bn == 0 && (g_force_bn == 0 || g_force_bn == 256)) {
-      bn = 256;
-      total = int64_t(args.tiles_m) * ((N + 255) / 256);
-      full = 0;
-      want = g_force_splits;
-    }
-    if (want > num_kb) want = num_kb;
-    const int64_t cut = total - full;
-    if (want >= 2 && cut > 0 && cut * cg <= kCounterSlotWords) {
-      const int64_t per = (num_kb + want - 1) / want;
-      const int64_t splits = (num_kb + per - 1) / per;  // no empty range
-      if (splits >= 2) {
-        args.splits = int(splits);
-        args.kb_per_split = int(per);
-        args.full_items = int(full);
-        uint32_t* counters = nullptr;
-        rc = split_k_counters(&counters);
-        if (rc) return rc;
-        cudaMemPool_t pool = nullptr;
-        rc = split_k_pool(&pool);
-        if (rc) return rc;
-        const size_t ws_bytes = size_t(cut) * splits * cg * BM * bn * sizeof(uint32_t);
-        B200_CUDA_TRY(cudaMallocFromPoolAsync(&split_ws, ws_bytes, pool, stream));
-        args.counters = counters;
-        args.ws = static_cast<uint32_t*>(split_ws);
-      }
-    }
-    if (args.splits == 1) args.full_items = int(total);
-  }
-  rc = launch_kind(kind, epi, bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
-  if (split_ws) {
-    cudaError_t fe = cudaFreeAsync(split_ws, stream);  // stream-ordered: released after the kernel
-    if (rc == B200_OK && fe != cudaSuccess) rc = fail(B200_ERR_CUDA, "cudaFreeAsync: %s", cudaGetErrorString(fe));
-  }
-  return rc;
+  return launch_kind(kind, epi, bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
 }
 
 namespace {
@@ -1093,13 +910,6 @@ __global__ void split_tf32_kernel(const float* __restrict__ x, float* __restrict
   }
 }
 
-// Per-device scratch for the split planes; grows on demand and is kept until the process ends.
-struct SplitScratch {
-  std::mutex mu;
-  float* buf[64] = {nullptr};
-  size_t cap[64] = {0};
-} g_split;
-
 }  // namespace
 
 int split_tf32_into(const float* A, const float* B, float* scratch, int64_t M, int64_t N, int64_t K,
@@ -1142,28 +952,25 @@ int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int
   if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
   if (lda < K || ldb < (b_is_nk ? K : N) || ldc < N)
     return fail(B200_ERR_BAD_ARGUMENT, "a leading dimension is smaller than the row it spans");
-  int dev = 0;
-  B200_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 64) return fail(B200_ERR_UNSUPPORTED, "device ordinal %d is beyond the scratch table", dev);
+  // The split planes live for this call only: taken from the stream-ordered pool on `stream` and
+  // given back on `stream` right behind the GEMM, so calls on different streams (or from different
+  // host threads) never share scratch, and nothing is freed while a kernel may still read it.
   const size_t need = split_tf32_scratch_floats(M, N, K, b_is_nk) * sizeof(float);
-  float* scratch = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(g_split.mu);
-    if (g_split.cap[dev] < need) {
-      if (g_split.buf[dev]) B200_CUDA_TRY(cudaFree(g_split.buf[dev]));  // waits for kernels still using it
-      g_split.buf[dev] = nullptr;
-      g_split.cap[dev] = 0;
-      B200_CUDA_TRY(cudaMalloc(&g_split.buf[dev], need));
-      g_split.cap[dev] = need;
-    }
-    scratch = g_split.buf[dev];
-  }
+  cudaMemPool_t pool = nullptr;
+  int rc = scratch_pool(&pool);
+  if (rc) return rc;
+  void* mem = nullptr;
+  B200_CUDA_TRY(cudaMallocFromPoolAsync(&mem, need, pool, stream));
+  float* scratch = static_cast<float*>(mem);
   int64_t lda_p = 0, ldb_p = 0;
   float* pb = nullptr;
-  int rc = split_tf32_into(A, B, scratch, M, N, K, lda, ldb, b_is_nk, &lda_p, &ldb_p, &pb, stream);
-  if (rc) return rc;
-  return launch_umma_gemm(KIND_TF32, EPI_F32, scratch, pb, C, M, N, K, lda_p, ldb_p, ldc, b_is_nk, nullptr,
-                          nullptr, 0, stream, tail);
+  rc = split_tf32_into(A, B, scratch, M, N, K, lda, ldb, b_is_nk, &lda_p, &ldb_p, &pb, stream);
+  if (rc == B200_OK)
+    rc = launch_umma_gemm(KIND_TF32, EPI_F32, scratch, pb, C, M, N, K, lda_p, ldb_p, ldc, b_is_nk, nullptr, nullptr, 0,
+                          stream, tail);
+  const cudaError_t fe = cudaFreeAsync(mem, stream);  // stream-ordered: released after the kernels above
+  if (rc == B200_OK && fe != cudaSuccess) rc = fail(B200_ERR_CUDA, "cudaFreeAsync: %s", cudaGetErrorString(fe));
+  return rc;
 }
 
 }  // namespace b200

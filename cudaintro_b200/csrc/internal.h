@@ -62,9 +62,6 @@ int encode_operand_map(CUtensorMap* map, int kind, const void* base, int64_t row
 // Whether kernels are launched with programmatic stream serialisation (set_dependent_launch).
 bool dependent_launch_enabled();
 
-// Split-K of the single-CTA tensor-core kernels: 0 = automatic, 1 = never, n = cut K into n ranges.
-int set_split_k(int splits);
-
 // 1 (default) = GEMM kernels are launched with programmatic stream serialisation; 0 = plain launches.
 int set_dependent_launch(int enabled);
 

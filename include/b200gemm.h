@@ -171,16 +171,6 @@ int b200_set_store_policy(int register_stores);
  * stream order is kept.  0: plain launches.  For measurements; results do not depend on it. */
 int b200_set_dependent_launch(int enabled);
 
-/* Split-K of the tensor-core kernels (off by default).  n >= 2 asks for it: a product with fewer
- * tiles than SMs gets every tile cut along K into n ranges (single-CTA 256-wide tiles); a product
- * whose last wave of tiles is less than half full gets the tiles of that wave cut into up to n
- * ranges so that the idle SMs share them.  Each range parks its partial sums in a workspace taken
- * from the stream-ordered allocator (released after the kernel), and the range that finishes a
- * tile last adds them in range order and stores C.  0 or 1 = off: on the shapes measured so far
- * the exchange of partial sums cost more than the extra parallelism brought.  Integer results are
- * unaffected; floating-point sums are regrouped per range (same tolerance). */
-int b200_set_split_k(int splits);
-
 /* Symmetric absmax quantiser of a row-major fp32 [R, C] matrix to int8 (same shape):
  *   along = 0: scale[r] = max_c |x[r][c]| / 127  (R scales);  along = 1: per column (C scales);
  *   q = clamp(rint(x / scale), -127, 127), ties to even; an all-zero row/column gets scale 1.
@@ -229,11 +219,30 @@ int b200_linear(int dtype, const void* X, const void* W, const float* bias, void
  * every output line needs goes up whole (B; A for the column-major layout); the other one travels
  * in up to 16 slabs of rows (columns), each multiplied as soon as it has arrived and copied back
  * while the next is on its way, so with pinned buffers the call costs about its host-to-device
- * traffic.  Device workspace, three streams and their events are kept between calls and grow as
- * needed; b200_host_release() frees them.  Calls are serialised by a lock. */
+ * traffic.  Device workspace, three streams and their events are kept per device between calls
+ * (the device that is current when the call is made) and grow as needed; b200_host_release()
+ * frees those of the current device.  Calls on one device are serialised by a lock.  When the
+ * call returns, with or without an error, nothing it issued still touches A, B or C.
+ * Stands where the reference's bodies copy nothing (they fill on the device,
+ * quantization/GEMM_int8.cu:41-49); it is the host-memory form of the call at :51-56. */
 int b200_gemm_host(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                    int layout);
 int b200_host_release(void);
+
+/* Host-buffer products against weights that stay on the device: the usual shape of a linear
+ * layer, whose weights do not change between calls.  No counterpart in the reference.
+ *   b200_host_weights_upload  copies a row-major [K, N] matrix B of `dtype` (b200_dtype) from host
+ *                             memory to the current device once and returns a handle;
+ *   b200_gemm_host_weights    C[M, N] = A[M, K] * B for host buffers A and C (row-major, packed):
+ *                             slabs of A go up, are multiplied and their rows of C come down, all
+ *                             three overlapped (uploads and downloads use both directions of the
+ *                             host link at once), so a call costs about max(bytes of A, bytes of
+ *                             C) over the link.  The device that holds the weights must be current;
+ *   b200_host_weights_free    releases the device copy and the handle.
+ * Output types and the workspace are those of b200_gemm_host. */
+int b200_host_weights_upload(int dtype, const void* B, int64_t K, int64_t N, void** weights);
+int b200_gemm_host_weights(const void* weights, const void* A, void* C, int64_t M);
+int b200_host_weights_free(void* weights);
 
 /* Timing helper: runs `iters` back-to-back launches of one of the GEMMs above (packed leading
  * dimensions) on `stream` between two CUDA events, waits for them, and returns the elapsed

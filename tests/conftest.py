@@ -39,3 +39,15 @@ def device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(scope="session")
+def reference_tree():
+    """Root of a checkout of the reference project (CUDAINTRO_REFERENCE_TREE, or a directory called
+    `reference` beside the repository); tests that need it skip where there is none."""
+    from __graft_entry__ import reference_tree as find
+
+    tree = find()
+    if tree is None:
+        pytest.skip("no checkout of the reference project on this machine")
+    return tree

@@ -8,6 +8,7 @@ import subprocess
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CUDA_INCLUDE = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
 
 
 def declared_symbols():
@@ -44,8 +45,48 @@ def test_gemm_result_layout_matches_reference_record(tmp_path):
         'int main(){std::printf("%zu %zu %zu %zu %zu",sizeof(GemmResult),offsetof(GemmResult,name),'
         "offsetof(GemmResult,iters),offsetof(GemmResult,secs),offsetof(GemmResult,tflops));}\n")
     exe = tmp_path / "t"
-    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-I", CUDA_INCLUDE, str(src), "-o",
+                    str(exe)], check=True)
     assert subprocess.run([str(exe)], capture_output=True, text=True).stdout.split() == ["32", "0", "8", "16", "24"]
+
+
+def test_reference_driver_compiles_against_the_stand_in_header_alone(tmp_path, reference_tree):
+    """quantization/main.cu:8-31 uses CHECK_CUBLAS, GemmResult and the four run_gemm_* declarations
+    of its "gemm_common.h".  A quoted include looks beside the including file first, so the
+    reference's file is reached through a symbolic link in an empty directory: the only
+    gemm_common.h it can then find is this repository's include/gemm_common.h."""
+    link = tmp_path / "main_link.cu"
+    os.symlink(os.path.join(reference_tree, "quantization", "main.cu"), link)
+    obj = tmp_path / "main.o"
+    subprocess.run(["nvcc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I",
+                    os.path.join(ROOT, "include"), "-c", str(link), "-o", str(obj)], check=True)
+    syms = subprocess.run(["nm", "-u", str(obj)], capture_output=True, text=True, check=True).stdout
+    for dt in ("bf16", "fp16", "fp32", "int8"):
+        assert f"_Z13run_gemm_{dt}P13cublasContext" in syms
+
+
+def test_error_helpers_print_like_the_reference_and_exit(tmp_path):
+    """CHECK_CUDA / CHECK_CUBLAS (quantization/gemm_common.h:37-55): one line
+    "<CUDA|cuBLAS> error: <text> at <file>:<line>" on stderr, then exit(EXIT_FAILURE);
+    cublas_status_to_string (:10-35) spells the enumerator, unknown codes read CUBLAS_STATUS_UNKNOWN."""
+    src = tmp_path / "e.cpp"
+    src.write_text(
+        '#include "gemm_common.h"\n#include <cstring>\n'
+        "int main(int argc, char** argv) {\n"
+        '  if (std::strcmp(cublas_status_to_string(CUBLAS_STATUS_ARCH_MISMATCH), "CUBLAS_STATUS_ARCH_MISMATCH")) return 3;\n'
+        '  if (std::strcmp(cublas_status_to_string((cublasStatus_t)12345), "CUBLAS_STATUS_UNKNOWN")) return 4;\n'
+        "  CHECK_CUBLAS(CUBLAS_STATUS_SUCCESS);\n"
+        "  if (argc > 1) CHECK_CUBLAS(CUBLAS_STATUS_NOT_INITIALIZED);\n"
+        "  CHECK_CUDA(cudaErrorInvalidValue);\n"
+        "  return 0;\n}\n")
+    exe = tmp_path / "e"
+    cuda_lib = os.path.join(os.path.dirname(CUDA_INCLUDE), "lib64")
+    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-I", CUDA_INCLUDE, str(src), "-o",
+                    str(exe), "-L", cuda_lib, "-lcudart", f"-Wl,-rpath,{cuda_lib}"], check=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 1 and re.fullmatch(r"CUDA error: invalid argument at .*e\.cpp:8\n", r.stderr), r
+    r = subprocess.run([str(exe), "x"], capture_output=True, text=True)
+    assert r.returncode == 1 and re.fullmatch(r"cuBLAS error: CUBLAS_STATUS_NOT_INITIALIZED at .*e\.cpp:7\n", r.stderr), r
 
 
 def test_public_header_is_plain_c(tmp_path):
@@ -95,7 +136,6 @@ def test_policy_knobs_and_multi_gpu_entry_points_validate_arguments(cb):
     assert lib.b200_set_tile_policy(0, 96, 0) == 1
     assert lib.b200_set_tile_policy(0, 0, 100) == 1        # group rows: multiple of 256
     assert lib.b200_set_tile_policy(0, 0, 0) == 0
-    assert lib.b200_set_split_k(-1) == 1 and lib.b200_set_split_k(65) == 1 and lib.b200_set_split_k(0) == 0
     one = C.c_void_p(16)
     dests = (C.c_void_p * 9)(*[one] * 9)
     assert lib.b200_gemm_multi(capi.I8, one, one, dests, 9, None, None, 16, 16, 16, 0, 0, 0, None) == 1
@@ -107,6 +147,13 @@ def test_policy_knobs_and_multi_gpu_entry_points_validate_arguments(cb):
     assert lib.b200_peer_marker(None, 2, 0, 1, None) == 1
     assert lib.b200_peer_alloc(0, C.byref(C.c_void_p())) == 1
     assert lib.b200_ipc_export(None, None) == 1 and lib.b200_ipc_import(None, None) == 1
+    # host-buffer products against resident weights: pointers, sizes and dtype are checked first
+    h = C.c_void_p()
+    assert lib.b200_host_weights_upload(capi.I8, None, 16, 16, C.byref(h)) == 1
+    assert lib.b200_host_weights_upload(capi.I8, one, 0, 16, C.byref(h)) == 1
+    assert lib.b200_host_weights_upload(9, one, 16, 16, C.byref(h)) == 1
+    assert lib.b200_gemm_host_weights(None, one, one, 16) == 1
+    assert lib.b200_host_weights_free(None) == 0
     # the allocation-free entry point refuses oversized problems before touching the device
     assert lib.b200_gemm_f32_3xtf32_static(one, one, one, 4096, 4096, 4096, 0, 0, 0, 0, None) == 5
 

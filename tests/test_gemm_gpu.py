@@ -175,6 +175,46 @@ def test_int8_8192_checksums_and_linearity(cb, device):
     assert torch.equal(c1.sum(dim=1, dtype=torch.int64).double(), a.double() @ row_sum_b)
 
 
+def test_int8_8192_sampled_rows_vs_oracle(cb, oracle, device):
+    """int8 8192^3 (the shape the int8 metric is quoted on), uniform [-127, 127]: rows from the first,
+    an inner and the last tile rows of C, bit for bit against the oracle; the first 512 rows against
+    the one-thread-per-element kernel."""
+    import torch
+
+    n = 8192
+    g = torch.Generator(device=device).manual_seed(11)
+    a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device, generator=g)
+    b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device, generator=g)
+    c = cb.gemm_i8_i32(a, b)
+    cb.check_device()
+    rows = [0, 1, 127, 128, 255, 256, 4095, 4096, 6001, 8063, 8064, 8191]
+    want = oracle.gemm_i8_i32(a.cpu().numpy(), b.cpu().numpy(), n, n, n, oracle.ROW_MAJOR, rows)
+    assert np.array_equal(c[rows].cpu().numpy(), want)
+    assert torch.equal(c[:512], cb.gemm_naive(a[:512], b))
+
+
+def test_fp16_8192_normal_inputs_sampled_rows_vs_oracle(cb, oracle, device):
+    """fp16 8192^3 (the shape the fp16 metric is quoted on), N(0,1) inputs, fp32 accumulate, fp16 out:
+    relative Frobenius error <= 2e-3 against the oracle's fp32 sums on sampled rows, the first 1024
+    rows against the validation kernel, and two runs bit-identical."""
+    import torch
+
+    n = 8192
+    g = torch.Generator(device=device).manual_seed(12)
+    a = torch.randn((n, n), device=device, generator=g).to(torch.float16)
+    b = torch.randn((n, n), device=device, generator=g).to(torch.float16)
+    c = cb.gemm_f16(a, b)
+    c2 = cb.gemm_f16(a, b)
+    cb.check_device()
+    assert torch.equal(c.view(torch.int16), c2.view(torch.int16))
+    rows = [0, 127, 128, 255, 256, 4097, 8064, 8191] + list(range(5000, 5008))
+    _, o32 = oracle.gemm_h16(a.view(torch.int16).cpu().numpy().view(np.uint16),
+                             b.view(torch.int16).cpu().numpy().view(np.uint16), n, n, n, False, oracle.ROW_MAJOR, rows)
+    assert rel_fro(c[rows].float().cpu().numpy(), o32) <= TOL_F16
+    ref = cb.gemm_naive(a[:1024], b)
+    assert float((c[:1024].float() - ref).norm() / ref.norm()) <= TOL_F16
+
+
 def test_padding_of_c_is_left_untouched(cb, device):
     """ldc > N: the columns between N and ldc (and rows past M) must keep their canary value."""
     import torch
@@ -538,6 +578,49 @@ def test_host_buffer_entry_point_in_several_slabs(cb, oracle, device, layout_nam
     capi.lib.b200_host_release()
 
 
+def test_host_buffers_against_weights_kept_on_the_device(cb, oracle, device):
+    """b200_host_weights_upload / b200_gemm_host_weights: B goes up once, then several A of different
+    heights (one slab, several slabs with a ragged last one) are multiplied from host buffers.  int8
+    bit-exact against the oracle; the handle is refused once freed."""
+    from cudaintro_b200 import capi
+
+    rng = np.random.default_rng(33)
+    N, K = 400, 640
+    b = rng.integers(-127, 128, (K, N)).astype(np.int8)
+    w = capi.HostWeights(capi.I8, b, K, N)
+    for M in (48, 1300, 512):
+        a = rng.integers(-127, 128, (M, K)).astype(np.int8)
+        c = np.full((M, N), -3, dtype=np.int32)
+        w.matmul(a, c, M)
+        assert np.array_equal(c, oracle.gemm_i8_i32(a, b, M, N, K)), M
+    w.close()
+    capi.lib.b200_host_release()
+    assert capi.lib.b200_gemm_host_weights(None, a.ctypes.data, c.ctypes.data, 8) == 1
+
+
+def test_host_buffer_calls_keep_one_workspace_per_device(cb, oracle):
+    """With two GPUs visible, a host-buffer product on device 1 after one on device 0 must use
+    streams and buffers of device 1 (each device has a workspace of its own)."""
+    import torch
+    from cudaintro_b200 import capi
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    rng = np.random.default_rng(34)
+    M, N, K = 640, 256, 384
+    a = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    b = rng.integers(-127, 128, (K, N)).astype(np.int8)
+    want = oracle.gemm_i8_i32(a, b, M, N, K)
+    for dev in (0, 1, 0):
+        with torch.cuda.device(dev):
+            c = np.zeros((M, N), dtype=np.int32)
+            cb.gemm_host(capi.I8, a, b, c, M, N, K)
+            assert np.array_equal(c, want), dev
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            capi.lib.b200_host_release()
+
+
 def test_suite_entry_points_keep_the_reference_protocol(cb, device, monkeypatch):
     """run_gemm_* (quantization/gemm_common.h:64-67) through their C++ symbols: name, iteration
     count in multiples of 256, and the reference's TFLOP/s formula (GEMM_int8.cu:80-84)."""
@@ -560,6 +643,32 @@ def test_suite_entry_points_keep_the_reference_protocol(cb, device, monkeypatch)
         assert r.iters >= 256 and r.iters % 256 == 0
         assert r.secs >= 0.2
         assert abs(r.tflops - 2.0 * 4096 ** 3 * r.iters / (r.secs * 1e12)) <= 1e-9 * r.tflops
+
+
+def test_reference_driver_binary_runs_on_this_library(cb, device):
+    """The reference's own host driver (quantization/main.cu:8-31), compiled unchanged against
+    include/gemm_common.h and linked with libb200gemm by `make -C oracle suite`: it must exit 0 and
+    print its four result lines (main.cu:24-26) in the driver's order BF16, FP16, FP32, INT8."""
+    import re
+    import subprocess
+
+    exe = os.path.join(os.path.dirname(GOLDEN), os.pardir, "oracle", "_ref", "gemm_suite_b200")
+    exe = os.path.normpath(exe)
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/gemm_suite_b200 was not built on a machine with the reference tree")
+    env = dict(os.environ, GEMM_SUITE_SECONDS="0.2")
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=300, env=env)
+    assert res.returncode == 0, res.stdout + res.stderr
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("Ran ")]
+    assert len(lines) == 4, res.stdout
+    for ln, name in zip(lines, ("BF16", "FP16", "FP32", "INT8")):
+        m = re.fullmatch(r"Ran (\d+) (\w+) GEMMs in ([0-9.eE+-]+) s \(([0-9.eE+-]+) TFLOP/s\)", ln)
+        assert m and m.group(2) == name, ln
+        iters, secs, tflops = int(m.group(1)), float(m.group(3)), float(m.group(4))
+        assert iters >= 256 and iters % 256 == 0 and secs >= 0.2
+        assert abs(tflops - 2.0 * 4096 ** 3 * iters / (secs * 1e12)) <= 2e-3 * tflops  # printed with 6 digits
+    for name in ("BF16", "FP16", "FP32", "INT8"):
+        assert f"Running {name}..." in res.stdout
 
 
 # ------------------------------------------------------------------ tile policies (single CTAs vs CTA pairs)

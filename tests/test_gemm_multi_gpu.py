@@ -109,42 +109,12 @@ def test_multi_destination_gemm_on_one_gpu(cb, oracle, device, policies, registe
         assert np.array_equal(o.view(torch.int16).cpu().numpy().view(np.uint16), want16)
 
 
-@pytest.fixture
-def split_k(cb):
-    from cudaintro_b200 import capi
-
-    yield capi.set_split_k
-    capi.set_split_k(0)
-
-
-@pytest.mark.parametrize("splits", [0, 1, 2, 5, 16])
-@pytest.mark.parametrize("shape", [(16, 512, 4112), (128, 1040, 2048), (1, 256, 1024), (130, 272, 8192)])
-def test_split_k_int8_and_w8a8_bit_exact(cb, oracle, device, split_k, shape, splits):
-    import torch
-
-    M, N, K = shape
-    rng = np.random.default_rng(M + N + K + splits)
-    a = rng.integers(-127, 128, (M, K)).astype(np.int8)
-    b = rng.integers(-127, 128, (K, N)).astype(np.int8)
-    sx = rng.uniform(0.001, 0.02, M).astype(np.float32)
-    sw = rng.uniform(0.001, 0.02, N).astype(np.float32)
-    split_k(splits)
-    ad, bd = to_dev(a, device), to_dev(b, device)
-    for _ in range(2):  # twice: the tile counters must be back at zero after a launch
-        c = cb.gemm_i8_i32(ad, bd)
-        cb.check_device()
-        assert np.array_equal(c.cpu().numpy(), oracle.gemm_i8_i32(a, b, M, N, K))
-    cw = cb.gemm_w8a8_bf16(ad, bd, to_dev(sx, device), to_dev(sw, device))
-    cb.check_device()
-    assert np.array_equal(cw.view(torch.int16).cpu().numpy().view(np.uint16), oracle.gemm_w8a8_bf16(a, b, sx, sw, M, N, K))
-
-
 @pytest.mark.parametrize("cg", [0, 1])
 @pytest.mark.parametrize("shape", [(4096, 4096, 1024), (4000, 4704, 1152), (2304, 6400, 2048)])
-def test_cut_last_wave_int8_and_w8a8_bit_exact(cb, device, policies, split_k, shape, cg):
-    """Shapes whose tiles leave the last wave of the persistent grid less than half full: with split-K
-    requested those tiles are cut along K (CTA pairs with cg = 0, single CTAs with cg = 1).  Checked
-    in full against the one-thread-per-element kernel, with the cut off (1) and on (2, 4 ranges)."""
+def test_partly_filled_last_wave_int8_and_w8a8_bit_exact(cb, device, policies, shape, cg):
+    """Shapes whose tiles leave the last wave of the persistent grid less than half full (CTA pairs
+    with cg = 0, single CTAs with cg = 1), checked in full against the one-thread-per-element
+    kernel, twice (the second launch starts from the state the first one left)."""
     import torch
 
     set_tiles, _ = policies
@@ -157,33 +127,13 @@ def test_cut_last_wave_int8_and_w8a8_bit_exact(cb, device, policies, split_k, sh
     want = cb.gemm_naive(a, b)
     want_w = ((want.float() * rs[:, None]) * cs[None, :]).to(torch.bfloat16)
     set_tiles(cg, 256 if cg else 0, 0)
-    for mode in (1, 2, 4):
-        split_k(mode)
-        for _ in range(2):  # twice: the counters of the cut tiles must be back at zero
-            c = cb.gemm_i8_i32(a, b)
-            cb.check_device()
-            assert torch.equal(c, want), (mode,)
-        cw = cb.gemm_w8a8_bf16(a, b, rs, cs)
+    for _ in range(2):
+        c = cb.gemm_i8_i32(a, b)
         cb.check_device()
-        assert torch.equal(cw.view(torch.int16), want_w.view(torch.int16)), (mode,)
-
-
-@pytest.mark.parametrize("M", [16, 128])
-@pytest.mark.parametrize("splits", [0, 1, 3])
-def test_split_k_fp16_linear_layer(cb, device, split_k, M, splits):
-    import torch
-
-    K, N = 4096, 11008
-    g = torch.Generator(device=device).manual_seed(M + splits)
-    x = torch.randn((M, K), device=device, generator=g).to(torch.float16)
-    w = (torch.randn((K, N), device=device, generator=g) * 0.02).to(torch.float16)
-    split_k(splits)
-    y = cb.gemm_f16(x, w)
-    y2 = cb.gemm_f16(x, w)
+        assert torch.equal(c, want)
+    cw = cb.gemm_w8a8_bf16(a, b, rs, cs)
     cb.check_device()
-    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))  # ranges are added in a fixed order
-    ref = cb.gemm_naive(x, w)
-    assert float((y.float() - ref).norm() / ref.norm()) <= 2e-3
+    assert torch.equal(cw.view(torch.int16), want_w.view(torch.int16))
 
 
 def test_completion_marker_passes_when_all_flags_arrive_and_gives_up_when_one_never_does(cb, oracle, device):
