@@ -13,7 +13,7 @@ import importlib
 
 _CAPI_NAMES = (
     "B200Error", "COL_MAJOR_NN", "F32_3XTF32", "F32_FFMA", "F32_TF32", "ROW_MAJOR", "ROW_MAJOR_BT", "check_device", "fill",
-    "gemm_bf16", "gemm_f16", "gemm_f32", "gemm_host", "gemm_i8_i32", "gemm_naive", "gemm_w8a8_bf16", "lib", "linear",
+    "gemm_16_f32", "gemm_bf16", "gemm_f16", "gemm_f32", "gemm_host", "gemm_i8_i32", "gemm_naive", "gemm_w8a8_bf16", "lib", "linear",
     "quantize_absmax", "set_tile_policy", "time_gemm",
 )
 

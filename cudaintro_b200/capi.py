@@ -29,6 +29,7 @@ SIGNATURES = {
     "b200_gemm_i8_i32": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
     "b200_gemm_bf16": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
     "b200_gemm_f16": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
+    "b200_gemm_16_f32": (_int, [_int, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
     "b200_gemm_f32": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _p]),
     "b200_gemm_f32_3xtf32_static": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _p]),
     "b200_gemm_w8a8_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p]),
@@ -143,6 +144,15 @@ def gemm_f16(a, b, layout=ROW_MAJOR, out=None):
 
     assert a.dtype == torch.float16 and b.dtype == torch.float16
     return _gemm(lib.b200_gemm_f16, a, b, torch.float16, layout, out)
+
+
+def gemm_16_f32(a, b, layout=ROW_MAJOR, out=None):
+    """fp16 or bf16 operands, fp32 accumulate, fp32 result (the sums, unrounded)."""
+    import torch
+
+    assert a.dtype == b.dtype and a.dtype in (torch.float16, torch.bfloat16)
+    code = F16 if a.dtype == torch.float16 else BF16
+    return _gemm(lambda *args: lib.b200_gemm_16_f32(code, *args), a, b, torch.float32, layout, out)
 
 
 def gemm_f32(a, b, layout=ROW_MAJOR, mode=F32_FFMA, out=None):

@@ -249,6 +249,13 @@ extern "C" int b200_gemm_f16(const void* A, const void* B, void* C, int64_t M, i
                              int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream) {
   return gemm_tensor(KIND_F16, EPI_F16, A, B, C, M, N, K, lda, ldb, ldc, layout, nullptr, nullptr, stream);
 }
+extern "C" int b200_gemm_16_f32(int dtype, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
+                                int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream) {
+  if (dtype != B200_F16 && dtype != B200_BF16)
+    return fail(B200_ERR_BAD_ARGUMENT, "b200_gemm_16_f32: dtype %d is neither B200_F16 nor B200_BF16", dtype);
+  return gemm_tensor(dtype == B200_F16 ? KIND_F16 : KIND_BF16, EPI_F32, A, B, C, M, N, K, lda, ldb, ldc, layout,
+                     nullptr, nullptr, stream);
+}
 extern "C" int b200_gemm_w8a8_bf16(const int8_t* A, const int8_t* B, const float* row_scale,
                                    const float* col_scale, void* C, int64_t M, int64_t N, int64_t K,
                                    int64_t lda, int64_t ldb, int64_t ldc, void* stream) {

@@ -869,9 +869,11 @@ int launch_kind(int kind, int epi, int bn, int cg, bool b_is_nk, const void* A, 
       break;
     case KIND_F16:
       if (epi == EPI_F16) return launch_bn<KIND_F16, EPI_F16>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_F32) return launch_bn<KIND_F16, EPI_F32>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
       break;
     case KIND_BF16:
       if (epi == EPI_BF16) return launch_bn<KIND_BF16, EPI_BF16>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_F32) return launch_bn<KIND_BF16, EPI_F32>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
       break;
     case KIND_TF32:  // A and B are the stacked low/high planes made by launch_sgemm_3xtf32
       if (epi == EPI_F32) return launch_bn<KIND_TF32, EPI_F32>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);

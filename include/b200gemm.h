@@ -56,6 +56,9 @@ typedef enum b200_f32_mode {
                           Needs lda, ldb multiples of 4 and 16-byte aligned A, B                */
 } b200_f32_mode;
 
+/* Element types of the operands. */
+typedef enum b200_dtype { B200_I8 = 0, B200_F16 = 1, B200_BF16 = 2, B200_F32 = 3 } b200_dtype;
+
 /* Text of the most recent failure on the calling thread ("" if none). */
 const char* b200_last_error(void);
 
@@ -92,6 +95,15 @@ int b200_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, 
  * CUBLAS_COMPUTE_32F) at quantization/GEMM_fp16.cu:51-56, :64-69. */
 int b200_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                   int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream);
+
+/* fp16 x fp16 or bf16 x bf16 (dtype = B200_F16 / B200_BF16), fp32 accumulate, fp32 out: the sums
+ * are stored unrounded.  Replaces the WMMA kernels behind launchMatrixMulTensorCores and
+ * launchMatrixMulTensorCoresBfloat16 (TileProgramming/matmulTensor.cu:31-48, :51-68, wrappers
+ * :71-87), which take half / __nv_bfloat16 operands and write float; C++ shims with those
+ * wrappers' names and signatures are in include/tile_programming.h.  Alignment rules of the
+ * 16-bit entry points above. */
+int b200_gemm_16_f32(int dtype, const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
+                     int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream);
 
 /* fp32 GEMM.  Replaces cublasGemmEx(CUDA_R_32F ..., CUBLAS_COMPUTE_32F) at
  * quantization/GEMM_fp32.cu:49-54, :62-67, and the tiled kernel launched at
@@ -188,7 +200,6 @@ int b200_fill_f32(float* data, int64_t count, uint64_t seed, float lo, float hi,
 /* Validation kernels: one thread per element of C, k ascending, no tensor cores, no tiling.
  * `dtype` is a b200_dtype; out is int32 for B200_I8, fp32 sums (not rounded) for the others.
  * They exist so that a full-size result of the fast kernels can be compared on the device. */
-typedef enum b200_dtype { B200_I8 = 0, B200_F16 = 1, B200_BF16 = 2, B200_F32 = 3 } b200_dtype;
 int b200_gemm_naive(int dtype, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, int layout, void* stream);
 

@@ -296,6 +296,40 @@ def test_16bit_vs_oracle(cb, oracle, device, shape, layout_name, is_bf16):
     assert np.all(np.abs(got - widen(o16)) <= 2 * ulp + 1e-3)
 
 
+@pytest.mark.parametrize("is_bf16", [True, False])
+@pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "COL_MAJOR_NN", "ROW_MAJOR_BT"])
+@pytest.mark.parametrize("shape", [(128, 256, 512), (200, 328, 1000), (1024, 1024, 1024), (16, 72, 64)])
+def test_16bit_operands_fp32_result(cb, oracle, device, shape, layout_name, is_bf16):
+    """b200_gemm_16_f32: 16-bit operands, the fp32 sums stored unrounded.  Products of two 16-bit
+    floats are exact in fp32, so the result differs from the oracle's fp32 sums only by the order of
+    the fp32 additions (and the tensor cores' alignment of addends): relative Frobenius error <= 2e-5."""
+    import torch
+
+    layout = getattr(cb, layout_name)
+    M, N, K = shape
+    if layout == cb.COL_MAJOR_NN:
+        M = (M + 7) // 8 * 8
+    else:
+        N = (N + 7) // 8 * 8 if layout == cb.ROW_MAJOR else N
+    K = (K + 7) // 8 * 8
+    rng = np.random.default_rng(M * 7 + N * 3 + K + int(is_bf16))
+    sa, sb = storage_shapes(cb, M, N, K, layout)
+    af = rng.standard_normal(sa).astype(np.float32)
+    bf = rng.standard_normal(sb).astype(np.float32)
+    if is_bf16:
+        a16, b16, dt = oracle.f32_to_bf16_bits(af), oracle.f32_to_bf16_bits(bf), torch.bfloat16
+    else:
+        a16, b16, dt = af.astype(np.float16).view(np.uint16), bf.astype(np.float16).view(np.uint16), torch.float16
+    c = cb.gemm_16_f32(to_dev(a16.view(np.int16), device, dt), to_dev(b16.view(np.int16), device, dt), layout)
+    cb.check_device()
+    assert c.dtype == torch.float32
+    if layout == cb.ROW_MAJOR_BT:
+        _, o32 = oracle.gemm_h16(a16, np.ascontiguousarray(b16.T), M, N, K, is_bf16, oracle.ROW_MAJOR)
+    else:
+        _, o32 = oracle.gemm_h16(a16, b16, M, N, K, is_bf16, layout)
+    assert rel_fro(c.cpu().numpy(), o32) <= 2e-5
+
+
 def test_bf16_config_8192_normal_inputs(cb, oracle, device):
     """bf16 8192^3, N(0,1) inputs, fp32 accumulate, bf16 out; relative Frobenius error <= 1e-2
     against the fp32 reference on sampled rows; whole matrix against the validation kernel."""
