@@ -139,30 +139,36 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- workload set-up
 
-def make_inputs(kind, M_local, N, K, device, seed):
-    """Seeded synthetic inputs of the workload's distributions, resident on the device."""
+def make_inputs(kind, M_local, N, K, device, seed, only_a=False):
+    """Seeded synthetic inputs of the workload's distributions, resident on the device.  A (this
+    rank's rows) depends on `seed`; B is the same on every rank.  only_a: B is not generated
+    (returned as None)."""
     import torch
 
     g = torch.Generator(device=device).manual_seed(seed)
-    extra = {}
+    gb = torch.Generator(device=device).manual_seed(999)
+    extra, b = {}, None
     if kind in ("bf16", "f16"):
         dt = torch.bfloat16 if kind == "bf16" else torch.float16
         a = torch.randn((M_local, K), device=device, generator=g).to(dt)
-        b = torch.randn((K, N), device=device, generator=torch.Generator(device=device).manual_seed(999)).to(dt)
+        if not only_a:
+            b = torch.randn((K, N), device=device, generator=gb).to(dt)
     elif kind == "i8":
         a = torch.randint(-127, 128, (M_local, K), dtype=torch.int8, device=device, generator=g)
-        b = torch.randint(-127, 128, (K, N), dtype=torch.int8, device=device,
-                          generator=torch.Generator(device=device).manual_seed(999))
+        if not only_a:
+            b = torch.randint(-127, 128, (K, N), dtype=torch.int8, device=device, generator=gb)
     else:  # w8a8: quantise N(0,1) fp32 sources with the library's own quantiser
         import cudaintro_b200 as cb
 
         x = torch.randn((M_local, K), device=device, generator=g)
         a, rs = cb.quantize_absmax(x, 0)
         del x
-        w = torch.randn((K, N), device=device, generator=torch.Generator(device=device).manual_seed(999))
-        b, cs = cb.quantize_absmax(w, 1)
-        del w
-        extra = {"row_scale": rs, "col_scale": cs}
+        extra = {"row_scale": rs}
+        if not only_a:
+            w = torch.randn((K, N), device=device, generator=gb)
+            b, cs = cb.quantize_absmax(w, 1)
+            del w
+            extra["col_scale"] = cs
     return a, b, extra
 
 
@@ -183,6 +189,49 @@ def launch(kind, a, b, c_slab, extra):
         cb.gemm_i8_i32(a, b, out=c_slab)
     else:
         cb.gemm_w8a8_bf16(a, b, extra["row_scale"], extra["col_scale"], out=c_slab)
+
+
+# ----------------------------------------------------------------------------- parity of the sharded result
+
+def sharded_rows_parity(kind, c_full, b, extra, M, N, K, world, device):
+    """Rank 0, outside any timed region: rows of the assembled C from EVERY rank's slab (first, last
+    and one inner row of each) against the CPU oracle.  The other ranks' rows of A are regenerated
+    here from their seeds (make_inputs is deterministic per seed and shape).  Bit-exact for the
+    integer kinds; relative Frobenius error within the stated tolerance for bf16 / fp16.  Raises
+    SystemExit on a mismatch; returns a short description otherwise."""
+    import numpy as np
+    import torch
+
+    import oracle as O
+
+    slot = -(-M // world)
+    checked = 0
+    for r in range(world):
+        row0 = min(M, r * slot)
+        rows_r = max(0, min(M, (r + 1) * slot) - row0)
+        if rows_r == 0:
+            continue
+        a_r, _, extra_r = make_inputs(kind, rows_r, N, K, device, seed=1234 + r, only_a=True)
+        local = sorted({0, rows_r // 2, rows_r - 1})
+        got = c_full[[row0 + i for i in local]].cpu()
+        a_np = a_r[local].cpu()
+        if kind == "i8":
+            want = O.gemm_i8_i32(a_np.numpy(), b.cpu().numpy(), len(local), N, K)
+            ok = np.array_equal(got.numpy(), want)
+        elif kind == "w8a8":
+            want = O.gemm_w8a8_bf16(a_np.numpy(), b.cpu().numpy(), extra_r["row_scale"][local].cpu().numpy(),
+                                    extra["col_scale"].cpu().numpy(), len(local), N, K)
+            ok = np.array_equal(got.view(torch.int16).numpy().view(np.uint16), want)
+        else:
+            _, o32 = O.gemm_h16(a_np.view(torch.int16).numpy().view(np.uint16),
+                                b.cpu().view(torch.int16).numpy().view(np.uint16), len(local), N, K, kind == "bf16")
+            err = float(np.linalg.norm(got.float().numpy().astype(np.float64) - o32) / np.linalg.norm(o32))
+            ok = err <= (1e-2 if kind == "bf16" else 2e-3)
+        if not ok:
+            raise SystemExit(f"sharded {kind} GEMM: rows {local} of rank {r}'s slab differ from the CPU oracle")
+        checked += len(local)
+        del a_r, extra_r
+    return f"oracle rows ok ({checked} rows, {min(3, slot)} from each of {world} slabs)"
 
 
 # ----------------------------------------------------------------------------- CPU legs
@@ -304,6 +353,104 @@ def reference_arm(args, wl_name):
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------------------------------------- the sharded W8A8 configuration
+
+def timed_ms(fn, steps, barrier, warmup=3):
+    """Average milliseconds per call of `fn` over `steps` back-to-back calls (CUDA events on the
+    current stream), after `warmup` untimed calls and a barrier."""
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def w8a8_sharded_record(world, rank, device, steps, barrier, max_over_ranks):
+    """The row-sharded W8A8 linear (M=8192, N=28672, K=8192, bf16 out, C complete on every rank) on
+    the GPUs of this run, whatever the main workload is: fused step, GEMM phase alone, NCCL
+    all-gather alone, and the one-GPU time of the whole product measured on rank 0 in the same run,
+    from which eff_compute = T1 / (G * T_gemm) and eff_e2e = T1 / (G * T_step) follow.  The
+    assembled C is checked against the CPU oracle (rank 0, untimed) before anything is timed."""
+    import torch
+
+    import cudaintro_b200 as cb
+    from cudaintro_b200 import capi
+    from cudaintro_b200.sharded import FusedShardedGemm, ShardedGemm
+
+    kind, M, N, K, in_b, out_b, unit = WORKLOADS["w8a8"]
+    sharded = ShardedGemm(M, N, torch.bfloat16, device)
+    M_local = sharded.part.rows
+    a, b, extra = make_inputs(kind, M_local, N, K, device, seed=1234 + rank)
+    ops = 2.0 * M * N * K
+    rec = {"workload": "w8a8", "M": M, "N": N, "K": K, "n_gpus": world, "steps": steps, "unit": unit}
+
+    def gemm_only():
+        launch(kind, a, b, sharded.c_slab, extra)
+
+    if world == 1:
+        gemm_only()
+        cb.check_device()
+        rec["parity"] = sharded_rows_parity(kind, sharded.result(), b, extra, M, N, K, 1, device)
+        t1 = timed_ms(gemm_only, steps, barrier)
+        cb.check_device()
+        rec.update({"one_gpu_ms": t1, "step_ms": t1, "gemm_phase_ms": t1, "value": ops / (t1 * 1e-3) / 1e12,
+                    "eff_compute": 1.0, "eff_e2e": 1.0})
+        return rec
+
+    fused = FusedShardedGemm(M, N, torch.bfloat16, device)
+
+    def fused_step():
+        fused.step(capi.W8A8, a, b, extra["row_scale"], extra["col_scale"])
+
+    sharded.step(lambda slab: launch(kind, a, b, slab, extra))
+    fused_step()
+    cb.check_device()
+    barrier()
+    if not torch.equal(fused.result().view(torch.int16), sharded.result().view(torch.int16)):
+        raise SystemExit(f"rank {rank}: W8A8 fused GEMM + all-gather differs from GEMM + NCCL all-gather")
+    if rank == 0:
+        rec["parity"] = sharded_rows_parity(kind, fused.result(), b, extra, M, N, K, world, device)
+    barrier()
+    step_ms = timed_ms(fused_step, steps, barrier)
+    cb.check_device()
+    barrier()
+    gemm_ms = timed_ms(gemm_only, steps, barrier)
+    barrier()
+    gather_ms = timed_ms(sharded.gather, steps, barrier)
+    barrier()
+    step_ms, gemm_ms, gather_ms = max_over_ranks([step_ms, gemm_ms, gather_ms])
+    # the whole product on one GPU (rank 0; the other ranks wait at the barrier)
+    t1 = 0.0
+    if rank == 0:
+        a_full = torch.cat([make_inputs(kind, sharded.part.slot_rows, N, K, device, seed=1234 + r, only_a=True)[0]
+                            for r in range(world)])[:M]
+        rs_full = torch.ones(M, device=device)
+        c_one = sharded.c_full[:M]
+        one = {"row_scale": rs_full, "col_scale": extra["col_scale"]}
+        t1 = timed_ms(lambda: launch(kind, a_full, b, c_one, one), steps, lambda: torch.cuda.synchronize())
+        del a_full
+    barrier()
+    (t1,) = max_over_ranks([t1])
+    c_bytes = M * N * out_b
+    rec.update({
+        "one_gpu_ms": t1, "step_ms": step_ms, "gemm_phase_ms": gemm_ms, "nccl_all_gather_ms": gather_ms,
+        "gemm_plus_nccl_all_gather_ms": gemm_ms + gather_ms, "value": ops / (step_ms * 1e-3) / 1e12,
+        "eff_compute": t1 / (world * gemm_ms), "eff_e2e": t1 / (world * step_ms),
+        "ingress_gbs": c_bytes * (world - 1) / world / (step_ms * 1e-3) / 1e9,
+        "nccl_bus_gbs": c_bytes * (world - 1) / world / (gather_ms * 1e-3) / 1e9,
+        "note": "step = multi-destination GEMM (every tile stored into every rank's C over NVLink) + completion "
+                "marker; every GPU receives (G-1)/G of C; eff_* against the one-GPU time of the same run"})
+    fused.close()
+    return rec
+
+
 # ----------------------------------------------------------------------------- main
 
 def main():
@@ -316,6 +463,7 @@ def main():
     ap.add_argument("--no-suite", action="store_true", help="skip the per-type side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-w8a8-record", action="store_true", help="skip the sharded W8A8 side record")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N>1: fused = the GEMM epilogue stores each tile into every rank's C over NVLink; "
                          "nccl = GEMM, then NCCL all-gather")
@@ -385,6 +533,16 @@ def main():
         if not torch.equal(fused.result().view(torch.uint8), sharded.result().view(torch.uint8)):
             raise SystemExit(f"rank {rank}: fused GEMM + all-gather differs from GEMM + NCCL all-gather")
 
+    # untimed check of the assembled C against the CPU oracle: rows from every rank's slab
+    parity = None
+    if True:
+        if fused is None:
+            nccl_step()
+            barrier()
+        if rank == 0:
+            parity = sharded_rows_parity(kind, (fused or sharded).result(), b, extra, M, N, K, world, device)
+        barrier()
+
     clocks = ClockSampler(local_rank, enabled=(rank == 0 and args.clock_sampling != "off"))
     for _ in range(max(args.warmup, 3)):
         step()
@@ -450,11 +608,21 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, gemm_ms, gather_ms, fused_kernel_ms = float(t[0]), float(t[1]), float(t[2]), float(t[3])
+    fused_in_step = fused is not None
 
     ops_step = 2.0 * M * N * K
     value = ops_step * args.steps / (ms * 1e-3) / 1e12
 
-    # ---- end to end through the host-buffer C entry point (pinned memory, copies timed)
+    def max_over_ranks(values):
+        tt = torch.tensor(values, device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return [float(x) for x in tt]
+
+    # ---- end to end through the host-buffer C entry points (pinned memory, copies timed).
+    # B (the operand every row of C needs; the weights of a linear layer) is uploaded once with
+    # b200_host_weights_upload, outside the timed region; a step then moves this rank's rows of A up
+    # and its rows of C down through b200_gemm_host_weights.
     e2e = None
     if kind != "w8a8" and not args.no_e2e:
         code = {"bf16": capi.BF16, "f16": capi.F16, "i8": capi.I8}[kind]
@@ -464,11 +632,10 @@ def main():
         ha.copy_(a)
         hb.copy_(b)
         e2e_steps = min(args.steps, 20)
+        weights = capi.HostWeights(code, hb, K, N)
 
         def host_call():
-            st = capi.lib.b200_gemm_host(code, ha.data_ptr(), hb.data_ptr(), hc.data_ptr(), M_local, N, K, cb.ROW_MAJOR)
-            if st:
-                raise cb.B200Error(st, capi.lib.b200_last_error().decode())
+            weights.matmul(ha, hc, M_local)
 
         for _ in range(3):
             host_call()
@@ -476,16 +643,47 @@ def main():
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
             host_call()
-        dt = time.perf_counter() - t0
-        tt = torch.tensor([dt], device=device, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dt = float(tt[0])
+        (dt,) = max_over_ranks([time.perf_counter() - t0])
+        # rows of the result against the device-side product of the same operands
+        # (bit for bit for int8; to rounding for the 16-bit types, whose K order depends on the tiling)
+        dev_rows = sharded.c_slab[:8].cpu()
+        same = torch.equal(hc[:8], dev_rows) if kind == "i8" else bool(
+            (hc[:8].float() - dev_rows.float()).norm() <= 1e-2 * dev_rows.float().norm())
+        if not same:
+            raise SystemExit(f"rank {rank}: host-buffer result differs from the device-buffer result")
         e2e = {"value": ops_step * e2e_steps / dt / 1e12, "unit": unit,
-               "h2d_bytes_per_step": world * (M_local * K + K * N) * in_b, "d2h_bytes_per_step": M * N * out_b,
+               "h2d_bytes_per_step": world * M_local * K * in_b, "d2h_bytes_per_step": M * N * out_b,
                "steps": e2e_steps, "ms_per_step": dt / e2e_steps * 1e3,
-               "api": "b200_gemm_host (pinned host buffers; on N>1 each rank moves its A rows, B and its C rows)"}
+               "api": "b200_gemm_host_weights (pinned host buffers; B uploaded once by b200_host_weights_upload "
+                      "before the timed region, every step moves each rank's rows of A up and its rows of C down)"}
+        if world == 1:  # the call that moves both operands every time, for comparison
+            def cold_call():
+                st = capi.lib.b200_gemm_host(code, ha.data_ptr(), hb.data_ptr(), hc.data_ptr(), M_local, N, K,
+                                             cb.ROW_MAJOR)
+                if st:
+                    raise cb.B200Error(st, capi.lib.b200_last_error().decode())
+
+            cold_call()
+            t0 = time.perf_counter()
+            for _ in range(5):
+                cold_call()
+            dt = (time.perf_counter() - t0) / 5
+            e2e["both_operands_every_step"] = {"value": ops_step / dt / 1e12, "ms_per_step": dt * 1e3,
+                                               "h2d_bytes_per_step": (M * K + K * N) * in_b, "api": "b200_gemm_host"}
+        weights.close()
         capi.lib.b200_host_release()
+        del ha, hb, hc
+
+    w8a8_rec = None
+    if not args.no_w8a8_record:
+        if fused is not None:
+            fused.close()
+            fused = None
+        if args.workload == "w8a8" and world == 1:
+            w8a8_rec = None  # the main line already is that measurement
+        else:
+            torch.cuda.empty_cache()
+            w8a8_rec = w8a8_sharded_record(world, rank, device, min(args.steps, 20), barrier, max_over_ranks)
 
     if rank != 0:
         if world > 1:
@@ -519,24 +717,29 @@ def main():
         "config": {"workload": args.workload, "M": M, "N": N, "K": K, "layout": "row-major",
                    "parallelism": f"rows of A over {world} GPU(s), B replicated" + (
                        "" if world == 1 else (", tiles stored into every rank's C by the GEMM epilogue (peer stores over NVLink)"
-                                              if fused is not None else ", NCCL all-gather of C")),
+                                              if fused_in_step else ", NCCL all-gather of C")),
                    "l2": "inputs larger than L2 (no flush needed)" if (M_local * K + K * N) * in_b > 126e6
                          else "inputs fit L2: back-to-back launches re-use it"},
         "roofline": roofline,
         "clocks": clocks.summary(),
         # kernels of this library launched inside the timed region, all ranks together: one GEMM per
         # rank and step, plus the completion-marker kernel when the epilogue does the gather
-        "gpu_launches": args.steps * world * (2 if fused is not None else 1),
+        "gpu_launches": args.steps * world * (2 if fused_in_step else 1),
         "frac_of_nominal_peak": value / world / NOMINAL_PEAK[kind],
     }
     if e2e is not None:
         line["e2e"] = e2e
+    if parity is not None:
+        line["parity"] = parity
+    if w8a8_rec is not None:
+        line["w8a8_sharded"] = w8a8_rec
     if world > 1:
         line["gemm_phase"] = {"ms": gemm_ms, "value": ops_step / (gemm_ms * 1e-3) / 1e12, "unit": unit,
                               "note": "all ranks' GEMMs without the all-gather"}
-        if fused is not None:
+        if fused_in_step:
             line["gemm_plus_nccl_all_gather_ms"] = gemm_ms + gather_ms
             line["fused_kernel_ms"] = fused_kernel_ms
+            line["fused_ingress_gbs"] = M * N * out_b * (world - 1) / world / (ms / args.steps * 1e-3) / 1e9
         c_bytes = M * N * out_b
         line["all_gather"] = {"ms": gather_ms, "bytes_received_per_gpu": c_bytes * (world - 1) // world,
                               "bus_gbs": c_bytes * (world - 1) / world / (gather_ms * 1e-3) / 1e9,

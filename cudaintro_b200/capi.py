@@ -47,6 +47,7 @@ SIGNATURES = {
     "b200_host_weights_free": (_int, [_p]),
     "b200_set_store_policy": (_int, [_int]),
     "b200_set_dependent_launch": (_int, [_int]),
+    "b200_test_lose_arrival": (_int, [_i64, C.c_uint64]),
     "b200_gemm_multi": (_int, [_int, _p, _p, C.POINTER(C.c_void_p), _int, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                _p]),
     "b200_peer_marker": (_int, [C.POINTER(C.c_void_p), _int, _int, C.c_uint32, _p]),

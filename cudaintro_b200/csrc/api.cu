@@ -500,6 +500,9 @@ extern "C" int b200_gemm_host_weights(const void* weights, const void* A, void* 
 
 extern "C" int b200_set_store_policy(int register_stores) { return set_store_policy(register_stores); }
 extern "C" int b200_set_dependent_launch(int enabled) { return set_dependent_launch(enabled); }
+extern "C" int b200_test_lose_arrival(int64_t k_block, uint64_t wait_budget_ns) {
+  return set_wait_test(k_block, wait_budget_ns);
+}
 
 extern "C" int b200_gemm_multi(int what, const void* A, const void* B, void* const* C_list, int n_dest,
                                const float* row_scale, const float* col_scale, int64_t M, int64_t N, int64_t K,

@@ -91,6 +91,11 @@ struct GemmArgs {
   int tiles_m, tiles_n;
   int group_m;  // m-tiles per group of the tile order
   int store_mode;  // StoreMode: how the epilogue writes C
+  // Bounded waits: how long one wait may last, and (for the test of the give-up path only) the
+  // k-block of CTA 0's first tile whose loads the producer leaves out, so that its "stage full"
+  // arrival never comes; -1 = none.
+  unsigned long long wait_budget_ns;
+  int lose_kb;
   int single_pass;  // tf32 kind only: 1 = plain fp32 operands, one pass (no split planes)
   const float* row_scale;
   const float* col_scale;
@@ -287,7 +292,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int kb = k_reversed ? num_kb - 1 - kin : kin;
           const int a_row0 = (X3 && pass != 0) ? p.M : 0;                       // plane 1 = high parts
           const int b_row0 = (X3 && pass != 1) ? (B_NK ? p.N : p.K) : 0;
-          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.wait_budget_ns)) { ok = false; break; }
+          if (kbt == p.lose_kb && it == 0 && blockIdx.x == 0) {
+            // Test of the give-up path: this stage is never filled and never announced, as if its
+            // arrival had been lost.  The MMA lane's wait for it runs out and the CTA drains.
+            if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
+            if (++kin == num_kb) { kin = 0; ++pass; }
+            continue;
+          }
           uint8_t* sa = smem + stage * T::STAGE_BYTES;
           uint8_t* sb = sa + T::A_BYTES;
           if constexpr (CG == 2) {
@@ -322,7 +334,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // Stay until every stage this CTA filled has been released: the releases are arrivals sent
         // by the leader's MMA commits into this CTA's shared memory, which must still exist.
         for (int i = 0; i < T::STAGES && ok; ++i) {
-          ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag);
+          ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.wait_budget_ns);
           if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -350,11 +362,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
         const int ab = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait_bounded(&acc_empty[ab], acc_phase ^ 1u, abort_flag)) break;
+        if (!mbar_wait_bounded(&acc_empty[ab], acc_phase ^ 1u, abort_flag, p.wait_budget_ns)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);
         for (int kb = 0; kb < total_kb; ++kb) {
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.wait_budget_ns)) { ok = false; break; }
           tc_fence_after_sync();
 #pragma unroll
           for (int j = 0; j < T::BK / T::UMMA_K; ++j) {
@@ -399,7 +411,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // One warp polls the barrier; all four then agree on the outcome, so that they always meet at
       // the same hardware barriers below even when the wait had to be given up.
       if (warp == 2) {
-        const bool ok = mbar_wait_bounded(&acc_full[ab], acc_phase, abort_flag);
+        const bool ok = mbar_wait_bounded(&acc_full[ab], acc_phase, abort_flag, p.wait_budget_ns);
         if (lane == 0) *epi_go = ok ? 1u : 0u;
       }
       named_barrier_sync(2, kEpiThreads);
@@ -648,6 +660,8 @@ int launch_major(bool b_nk, const void* A, const void* B, const GemmArgs& args, 
 
 int g_force_cg = 0, g_force_bn = 0, g_group_rows = 0;  // 0 = automatic; set through b200_set_tile_policy
 int g_force_store = 0;                                  // 0 = automatic, STORE_VECTOR = register stores
+unsigned long long g_wait_budget_ns = kWaitBudgetNs;    // per-wait limit handed to the kernels
+int g_lose_kb = -1;                                     // give-up test: k-block whose arrival is left out
 thread_local bool g_tf32_single_pass_call = false;      // set by launch_sgemm_tf32 around its launch
 
 // Stream-ordered memory pool for per-call scratch (the split planes of the 3xTF32 product), one per
@@ -724,6 +738,13 @@ int set_tile_policy(int cg, int bn, int group_rows) {
   g_force_cg = cg;
   g_force_bn = bn;
   g_group_rows = group_rows;
+  return B200_OK;
+}
+
+int set_wait_test(long long lose_kb, unsigned long long budget_ns) {
+  if (lose_kb < -1 || lose_kb > (1 << 20)) return fail(B200_ERR_BAD_ARGUMENT, "wait test: k-block out of range");
+  g_lose_kb = int(lose_kb);
+  g_wait_budget_ns = budget_ns ? budget_ns : kWaitBudgetNs;
   return B200_OK;
 }
 
@@ -811,6 +832,8 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   args.bias = tail.bias;
   args.tail_flags = tail.flags;
   args.single_pass = (kind == KIND_TF32 && g_tf32_single_pass_call) ? 1 : 0;
+  args.wait_budget_ns = g_wait_budget_ns;
+  args.lose_kb = g_lose_kb;
 
   int sms = 0;
   int rc = sm_count_of_current_device(&sms);

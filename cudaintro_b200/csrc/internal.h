@@ -62,6 +62,11 @@ int encode_operand_map(CUtensorMap* map, int kind, const void* base, int64_t row
 // Whether kernels are launched with programmatic stream serialisation (set_dependent_launch).
 bool dependent_launch_enabled();
 
+// Test of the give-up path of the tensor-core kernel: lose_kb >= 0 makes the next launches' first CTA
+// leave out the loads of that k-block of its first tile; budget_ns (0 = the default four seconds)
+// is how long a single device-side wait may last.  lose_kb = -1, budget_ns = 0 restores normal operation.
+int set_wait_test(long long lose_kb, unsigned long long budget_ns);
+
 // 1 (default) = GEMM kernels are launched with programmatic stream serialisation; 0 = plain launches.
 int set_dependent_launch(int enabled);
 

@@ -53,21 +53,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Longest any single wait may last before the kernel gives up (a whole GEMM takes milliseconds).
+// Longest any single wait may last before the kernel gives up (a whole GEMM takes milliseconds),
+// unless the caller passes a budget of its own.
 constexpr uint64_t kWaitBudgetNs = 4000000000ull;
 
 // Bounded wait on a phase of an mbarrier.  `abort_flag` is a shared-memory word that any role
 // of the CTA raises when its own wait ran out; every other role then leaves its wait too, so
 // that the CTA always reaches its final barrier and frees its tensor memory.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint64_t budget_ns = kWaitBudgetNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ffu) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+      if (global_timer_ns() - t0 > budget_ns) {
         *abort_flag = 1u;
         return false;
       }

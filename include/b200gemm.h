@@ -123,7 +123,10 @@ int b200_gemm_f32(const float* A, const float* B, float* C, int64_t M, int64_t N
  *   - Every GPU that loads the library holds the 32 MiB until the process exits.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current); make that first call before any stream
- *     capture begins.
+ *     capture begins.  With CUDA's lazy module loading that first call may also be the moment the
+ *     library's code, and the 32 MiB array with it, is placed on the device, so it can fail for
+ *     lack of memory: make it at start-up, before the host claims the rest of the device.  Calls
+ *     after the first take no device memory at all.
  *   - All calls on a device share the one array.  Each call rewrites every word it later reads,
  *     so nothing has to be cleared between calls, but two calls whose kernels overlap on the GPU
  *     (different streams, or different host threads) race on it: serialise them.
@@ -182,6 +185,16 @@ int b200_set_store_policy(int register_stores);
  * (griddepcontrol.wait) for that predecessor to complete before it touches global memory, so
  * stream order is kept.  0: plain launches.  For measurements; results do not depend on it. */
 int b200_set_dependent_launch(int enabled);
+
+/* Test hook for the kernels' failure handling (process-wide; not for production use).  Every
+ * device-side wait of the tensor-core kernel is bounded: a wait that outlasts its budget makes the
+ * CTA give up in an orderly way (all its roles leave, copies in flight land, tensor memory is
+ * freed), the kernel returns and b200_check_device reports B200_ERR_DEVICE_WAIT.  This call makes
+ * that happen without any fault: with k_block >= 0 the first CTA of every later launch leaves out
+ * the loads of that k-block of its first tile, as if their completion had been lost, and
+ * wait_budget_ns (0 = the default of four seconds) replaces the budget.  k_block = -1 with
+ * wait_budget_ns = 0 restores normal operation.  No counterpart in the reference. */
+int b200_test_lose_arrival(int64_t k_block, uint64_t wait_budget_ns);
 
 /* Symmetric absmax quantiser of a row-major fp32 [R, C] matrix to int8 (same shape):
  *   along = 0: scale[r] = max_c |x[r][c]| / 127  (R scales);  along = 1: per column (C scales);

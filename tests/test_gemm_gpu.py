@@ -716,6 +716,44 @@ def policy(cb):
 POLICY_SHAPES = [(256, 256, 128), (208, 336, 1008), (16, 512, 4112), (1024, 768, 2048), (257, 272, 64)]
 
 
+def test_kernel_gives_up_a_wait_that_cannot_end_and_the_device_stays_usable(cb, oracle, device, policy):
+    """Failure handling of the tensor-core kernel itself, without any fault: the producer of a
+    single-CTA launch leaves out the loads of one k-block (b200_test_lose_arrival), so the MMA
+    lane's bounded wait for that stage runs out after the 50 ms budget given here; the CTA drains,
+    the kernel returns, b200_check_device reports B200_ERR_DEVICE_WAIT, and the next product on the
+    same context is bit-exact again."""
+    import time
+
+    import torch
+    from cudaintro_b200 import capi
+
+    rng = np.random.default_rng(5)
+    M, N, K = 128, 256, 512
+    a = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    b = rng.integers(-127, 128, (K, N)).astype(np.int8)
+    ad, bd = to_dev(a, device), to_dev(b, device)
+    want = oracle.gemm_i8_i32(a, b, M, N, K)
+    policy(1, 256)  # the general kernel, one CTA, one tile
+    assert np.array_equal(cb.gemm_i8_i32(ad, bd).cpu().numpy(), want)
+    cb.check_device()
+    try:
+        capi._check(capi.lib.b200_test_lose_arrival(1, 50_000_000))
+        t0 = time.perf_counter()
+        cb.gemm_i8_i32(ad, bd)
+        with pytest.raises(cb.B200Error) as info:
+            cb.check_device()
+        waited = time.perf_counter() - t0
+        assert info.value.status == 4  # B200_ERR_DEVICE_WAIT
+        assert 0.04 <= waited < 2.0, waited
+    finally:
+        capi._check(capi.lib.b200_test_lose_arrival(-1, 0))
+    cb.check_device()  # the record was cleared by the failing check
+    for _ in range(2):
+        assert np.array_equal(cb.gemm_i8_i32(ad, bd).cpu().numpy(), want)
+    cb.check_device()
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("cg,bn", [(1, 256), (1, 128), (2, 256)])
 @pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "COL_MAJOR_NN", "ROW_MAJOR_BT"])
 @pytest.mark.parametrize("shape", POLICY_SHAPES)

@@ -59,6 +59,30 @@ def test_static_scratch_entry_point_matches_allocating_one(cb, oracle, device):
         assert rel_fro(out.cpu().numpy(), truth) <= TOL_F32
 
 
+def test_static_scratch_entry_point_takes_no_device_memory_after_its_first_call(cb, device):
+    """After one warm-up call on the device (which loads the library's code and the 32 MiB array
+    with it), further calls must leave the amount of free device memory exactly where it was:
+    nothing on their path allocates, not even from a pool.  Operands and results are created
+    before the measurement; the calls go through the C ABI only."""
+    import torch
+
+    from cudaintro_b200 import capi
+
+    M, N, K = 384, 264, 520
+    g = torch.Generator(device=device).manual_seed(7)
+    a = torch.rand((M, K), device=device, generator=g)
+    b = torch.rand((K, N), device=device, generator=g)
+    out = torch.empty((M, N), device=device)
+    call_static(capi, a, b, out, M, N, K, cb.ROW_MAJOR)  # first call: set-up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(device)
+    for _ in range(5):
+        call_static(capi, a, b, out, M, N, K, cb.ROW_MAJOR)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(device)
+    assert free_after == free_before
+
+
 def test_static_scratch_entry_point_refuses_what_does_not_fit(cb, device):
     import torch
 
