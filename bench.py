@@ -212,7 +212,14 @@ def sharded_rows_parity(kind, c_full, b, extra, M, N, K, world, device):
         if rows_r == 0:
             continue
         a_r, _, extra_r = make_inputs(kind, rows_r, N, K, device, seed=1234 + r, only_a=True)
-        local = sorted({0, rows_r // 2, rows_r - 1})
+        # first, last and an inner row of every slab; with one or two slabs also rows next to the 128- and
+        # 256-row tile edges and more inner rows (about 16 rows in all)
+        picks = {0, rows_r - 1, rows_r // 2}
+        if world <= 2:
+            picks |= {127, 128, 255, 256} | {(i * rows_r) // 6 for i in range(6)}
+        elif world == 4:
+            picks |= {255, 256}
+        local = sorted(i for i in picks if 0 <= i < rows_r)
         got = c_full[[row0 + i for i in local]].cpu()
         a_np = a_r[local].cpu()
         if kind == "i8":
@@ -231,7 +238,7 @@ def sharded_rows_parity(kind, c_full, b, extra, M, N, K, world, device):
             raise SystemExit(f"sharded {kind} GEMM: rows {local} of rank {r}'s slab differ from the CPU oracle")
         checked += len(local)
         del a_r, extra_r
-    return f"oracle rows ok ({checked} rows, {min(3, slot)} from each of {world} slabs)"
+    return f"oracle rows ok ({checked} rows from {world} slab(s), every rank's among them)"
 
 
 # ----------------------------------------------------------------------------- CPU legs
@@ -469,6 +476,11 @@ def main():
                          "nccl = GEMM, then NCCL all-gather")
     ap.add_argument("--clock-sampling", default="rank0", choices=["rank0", "off"],
                     help="rank0: a separate nvidia-smi process polls rank 0's GPU; off: no clock record")
+    ap.add_argument("--multi-tile", default="", metavar="CG,BN",
+                    help="force the tiling of every GEMM of the run (CTA grouping, tile width), e.g. 1,128; "
+                         "for measurements of the multi-destination epilogue")
+    ap.add_argument("--multi-staging", type=int, default=4, choices=[2, 4],
+                    help="output tiles staged per CTA by the multi-destination epilogue (4 = default of the library)")
     ap.add_argument("--register-stores", action="store_true",
                     help="write C straight from registers instead of staged TMA stores (for comparison)")
     args = ap.parse_args()
@@ -500,6 +512,11 @@ def main():
     kind, M, N, K, in_b, out_b, unit = WORKLOADS[args.workload]
     if args.register_stores:
         capi.set_store_policy(True)
+    if args.multi_staging != 4:
+        capi._check(capi.lib.b200_set_multi_staging(0))
+    if args.multi_tile:
+        cg_, bn_ = (int(x) for x in args.multi_tile.split(","))
+        cb.set_tile_policy(cg_, bn_, 0)
     from cudaintro_b200.sharded import ShardedGemm
 
     sharded = ShardedGemm(M, N, out_dtype(kind), device)

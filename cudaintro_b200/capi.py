@@ -48,6 +48,10 @@ SIGNATURES = {
     "b200_set_store_policy": (_int, [_int]),
     "b200_set_dependent_launch": (_int, [_int]),
     "b200_test_lose_arrival": (_int, [_i64, C.c_uint64]),
+    "b200_set_l2_hints": (_int, [_int]),
+    "b200_set_multi_staging": (_int, [_int]),
+    "b200_set_3xtf32_path": (_int, [_int]),
+    "b200_set_ffma_k_ranges": (_int, [_int]),
     "b200_gemm_multi": (_int, [_int, _p, _p, C.POINTER(C.c_void_p), _int, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                _p]),
     "b200_peer_marker": (_int, [C.POINTER(C.c_void_p), _int, _int, C.c_uint32, _p]),

@@ -270,7 +270,8 @@ extern "C" int b200_gemm_f32(const float* A, const float* B, float* C, int64_t M
   if (rc) return rc;
   if (mode == B200_F32_FFMA)
     return launch_sgemm_ffma(static_cast<const float*>(nv.A), static_cast<const float*>(nv.B), C, nv.M, nv.N,
-                             nv.K, nv.lda, nv.ldb, nv.ldc, nv.b_is_nk, static_cast<cudaStream_t>(stream));
+                             nv.K, nv.lda, nv.ldb, nv.ldc, nv.b_is_nk, static_cast<cudaStream_t>(stream), Tail(),
+                             /*may_split_k=*/true);
   if (mode == B200_F32_3XTF32)
     return launch_sgemm_3xtf32(static_cast<const float*>(nv.A), static_cast<const float*>(nv.B), C, nv.M, nv.N,
                                nv.K, nv.lda, nv.ldb, nv.ldc, nv.b_is_nk, static_cast<cudaStream_t>(stream));
@@ -500,6 +501,10 @@ extern "C" int b200_gemm_host_weights(const void* weights, const void* A, void* 
 
 extern "C" int b200_set_store_policy(int register_stores) { return set_store_policy(register_stores); }
 extern "C" int b200_set_dependent_launch(int enabled) { return set_dependent_launch(enabled); }
+extern "C" int b200_set_l2_hints(int hints) { return set_l2_hints(hints); }
+extern "C" int b200_set_multi_staging(int deep) { return set_deep_staging(deep); }
+extern "C" int b200_set_3xtf32_path(int path) { return set_x3_path(path); }
+extern "C" int b200_set_ffma_k_ranges(int ranges) { return set_ffma_ksplit(ranges); }
 extern "C" int b200_test_lose_arrival(int64_t k_block, uint64_t wait_budget_ns) {
   return set_wait_test(k_block, wait_budget_ns);
 }

@@ -50,11 +50,15 @@ constexpr int kThreads = 192;    // producer warp, MMA warp, four epilogue warps
 constexpr int kSmemBudget = 227 * 1024;
 
 bool g_use_pdl = true;  // launch the GEMM kernel with programmatic stream serialisation
+bool g_deep_staging = true;  // several destinations: stage four output tiles instead of two
 
 // CG = 1: one CTA owns a 128 x BN tile.  CG = 2: a pair of CTAs (cluster of 2) owns a 256 x BN tile;
 // each CTA stages its own 128 rows of A and its own BN/2 columns of B, and the even-ranked CTA
 // issues tcgen05.mma.cta_group::2 for both.
-template <int KIND, int BN_, int CG_ = 1>
+// NSTG = output tiles (128 rows x 128 bytes) staged for the TMA stores: 2 for one destination; 4 when
+// every tile goes to several GPUs, so that a CTA can drain a whole accumulator without waiting for
+// NVLink to take the previous boxes (the ring gives up one stage for it).
+template <int KIND, int BN_, int CG_ = 1, int NSTG_ = 2>
 struct Tile {
   static constexpr int ELEM = KIND == KIND_I8 ? 1 : (KIND == KIND_TF32 ? 4 : 2);
   static constexpr int BN = BN_;
@@ -68,7 +72,8 @@ struct Tile {
   static constexpr int B_BYTES = BN_CTA * 128;
   static constexpr int SPAN_BYTES = BK * 128;  // one span of B: BK k-rows of 128 bytes
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGING_BYTES = 2 * BM * 128;  // two 128-row x 128-byte output tiles for the TMA stores
+  static constexpr int NSTG = NSTG_;
+  static constexpr int STAGING_BYTES = NSTG * BM * 128;  // 128-row x 128-byte output tiles for the TMA stores
   static constexpr int STAGES_FIT = (kSmemBudget - 2048 - STAGING_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // BN is a power of two here
@@ -96,6 +101,9 @@ struct GemmArgs {
   // arrival never comes; -1 = none.
   unsigned long long wait_budget_ns;
   int lose_kb;
+  // L2 eviction hints, a bit set: 1 = the operand whose slab a group of tiles re-reads (A) is kept
+  // (evict last), 2 = the operand that streams past (B) goes first, 4 = so do the stores of C.
+  int l2_hints;
   int single_pass;  // tf32 kind only: 1 = plain fp32 operands, one pass (no split planes)
   const float* row_scale;
   const float* col_scale;
@@ -200,16 +208,16 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, 
   }
 }
 
-template <int KIND, int BN, bool B_NK, int EPI, int CG>
+template <int KIND, int BN, bool B_NK, int EPI, int CG, int NSTG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CMaps tmap_c, const GemmArgs p) {
-  using T = Tile<KIND, BN, CG>;
+  using T = Tile<KIND, BN, CG, NSTG>;
   constexpr int TILE_M = BM * CG;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes: align the stage ring to that.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* staging = smem + T::STAGES * T::STAGE_BYTES;  // two output tiles, 128 rows x 128 bytes each
+  uint8_t* staging = smem + T::STAGES * T::STAGE_BYTES;  // NSTG output tiles, 128 rows x 128 bytes each
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + T::STAGING_BYTES);
   uint64_t* full_bar = bars;                   // [STAGES] producer(s) -> MMA   (pair: the leader's is used)
   uint64_t* empty_bar = bars + T::STAGES;      // [STAGES] MMA -> producer      (pair: one in each CTA)
@@ -276,6 +284,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
+      const uint64_t pol_a = (p.l2_hints & 1) ? l2_policy_evict_last() : l2_policy_evict_normal();
+      const uint64_t pol_b = (p.l2_hints & 2) ? l2_policy_evict_first() : l2_policy_evict_normal();
       for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
         int mb, nb;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
@@ -306,24 +316,25 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // Both CTAs' bytes are credited to the leader's barrier; only the leader arms it.
             const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
             if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * T::STAGE_BYTES);
-            tma_load_2d_pair(sa, &tmap_a, bar, kb * T::BK, a_row0 + m0);
+            tma_load_2d_pair_hint(sa, &tmap_a, bar, kb * T::BK, a_row0 + m0, pol_a);
             if constexpr (B_NK) {
-              tma_load_2d_pair(sb, &tmap_b, bar, kb * T::BK, b_row0 + n0);
+              tma_load_2d_pair_hint(sb, &tmap_b, bar, kb * T::BK, b_row0 + n0, pol_b);
             } else {
 #pragma unroll
               for (int s = 0; s < T::NSPANS; ++s)
-                tma_load_2d_pair(sb + s * T::SPAN_BYTES, &tmap_b, bar, n0 + s * T::SPAN, b_row0 + kb * T::BK);
+                tma_load_2d_pair_hint(sb + s * T::SPAN_BYTES, &tmap_b, bar, n0 + s * T::SPAN, b_row0 + kb * T::BK,
+                                      pol_b);
             }
           } else {
             mbar_arrive_expect_tx(&full_bar[stage], T::STAGE_BYTES);
-            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * T::BK, a_row0 + m0);
+            tma_load_2d_hint(sa, &tmap_a, &full_bar[stage], kb * T::BK, a_row0 + m0, pol_a);
             if constexpr (B_NK) {
-              tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * T::BK, b_row0 + n0);
+              tma_load_2d_hint(sb, &tmap_b, &full_bar[stage], kb * T::BK, b_row0 + n0, pol_b);
             } else {
 #pragma unroll
               for (int s = 0; s < T::NSPANS; ++s)
-                tma_load_2d(sb + s * T::SPAN_BYTES, &tmap_b, &full_bar[stage], n0 + s * T::SPAN,
-                            b_row0 + kb * T::BK);
+                tma_load_2d_hint(sb + s * T::SPAN_BYTES, &tmap_b, &full_bar[stage], n0 + s * T::SPAN,
+                                 b_row0 + kb * T::BK, pol_b);
             }
           }
           if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
@@ -402,6 +413,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const bool store_thread = warp == 2 && lane == 0;
     uint32_t boxes = 0;
     int it = 0;
+    const uint64_t pol_c = (p.l2_hints & 4) ? l2_policy_evict_first() : l2_policy_evict_normal();
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mb, nb;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
@@ -430,8 +442,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int bx = 0; bx < BN / BOX_COLS; ++bx) {
           const int n0 = nb * BN + bx * BOX_COLS;
           if (n0 >= p.N) break;  // uniform across the four warps
-          uint8_t* buf = staging + (boxes & 1u) * (BM * 128);
-          if (store_thread) tma_store_wait_read<1>();  // the store that last used `buf` has read it
+          uint8_t* buf = staging + (boxes % uint32_t(NSTG)) * (BM * 128);
+          if (store_thread) tma_store_wait_read<NSTG - 1>();  // the stores that last used `buf` have read it
           named_barrier_sync(1, kEpiThreads);
 #pragma unroll
           for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
@@ -449,14 +461,19 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           fence_proxy_async_smem();
           named_barrier_sync(1, kEpiThreads);
           if (store_thread) {
-            // Start each tile at a different destination (rotating with the CTA and the tile count):
-            // when the destinations are peer GPUs, every sender then spreads its traffic over all
-            // receivers at all times instead of all senders hitting the same receiver together.
-            int g = int((uint32_t(first_tile) + boxes) % uint32_t(p.n_dest));
-            for (int i = 0; i < p.n_dest; ++i) {
-              tma_store_2d(&tmap_c.m[g], buf, n0, tile_row0);
-              if (++g == p.n_dest) g = 0;
+            // Destination 0 (by convention the local copy) goes last; the others (peer GPUs) are
+            // walked from a start that rotates with the CTA and the box count, so that every sender
+            // spreads its traffic over all receivers at all times instead of all senders hitting
+            // the same receiver together.
+            if (p.n_dest > 1) {
+              const int peers = p.n_dest - 1;
+              int g = 1 + int((uint32_t(first_tile) + boxes) % uint32_t(peers));
+              for (int i = 0; i < peers; ++i) {
+                tma_store_2d_hint(&tmap_c.m[g], buf, n0, tile_row0, pol_c);
+                if (++g == p.n_dest) g = 1;
+              }
             }
+            tma_store_2d_hint(&tmap_c.m[0], buf, n0, tile_row0, pol_c);
             tma_store_commit();
           }
           ++boxes;
@@ -574,11 +591,11 @@ int sm_count_of_current_device(int* out) {
   return B200_OK;
 }
 
-template <int KIND, int BN, bool B_NK, int EPI, int CG>
+template <int KIND, int BN, bool B_NK, int EPI, int CG, int NSTG = 2>
 int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb,
                cudaStream_t stream) {
-  using T = Tile<KIND, BN, CG>;
-  auto kernel = gemm_umma_kernel<KIND, BN, B_NK, EPI, CG>;
+  using T = Tile<KIND, BN, CG, NSTG>;
+  auto kernel = gemm_umma_kernel<KIND, BN, B_NK, EPI, CG, NSTG>;
   // The shared-memory attribute is per device: set it whenever this thread meets a new device.
   static thread_local int last_dev = -1;
   int dev = 0;
@@ -662,6 +679,7 @@ int g_force_cg = 0, g_force_bn = 0, g_group_rows = 0;  // 0 = automatic; set thr
 int g_force_store = 0;                                  // 0 = automatic, STORE_VECTOR = register stores
 unsigned long long g_wait_budget_ns = kWaitBudgetNs;    // per-wait limit handed to the kernels
 int g_lose_kb = -1;                                     // give-up test: k-block whose arrival is left out
+int g_l2_hints = -1;                                    // -1 = automatic, else the bit set of GemmArgs::l2_hints
 thread_local bool g_tf32_single_pass_call = false;      // set by launch_sgemm_tf32 around its launch
 
 // Stream-ordered memory pool for per-call scratch (the split planes of the 3xTF32 product), one per
@@ -700,6 +718,14 @@ int launch_bn(int bn, int cg, bool b_nk, const void* A, const void* B, GemmArgs 
   args.tiles_m = int((args.M + BM * cg - 1) / (BM * cg));
   args.group_m = (g_group_rows ? g_group_rows : kDefaultGroupRows) / (BM * cg);
   if (args.group_m < 1) args.group_m = 1;
+  // Several destinations (row-major B, the multi-GPU entry point): four staged output tiles.
+  if constexpr (EPI != EPI_F32) {
+    if (args.n_dest > 1 && !b_nk && args.store_mode == STORE_TMA && g_deep_staging) {
+      if (cg == 2 && bn == 256) return launch_one<KIND, 256, false, EPI, 2, 4>(A, B, args, lda, ldb, stream);
+      if (cg == 1 && bn == 256) return launch_one<KIND, 256, false, EPI, 1, 4>(A, B, args, lda, ldb, stream);
+      if (cg == 1 && bn == 128) return launch_one<KIND, 128, false, EPI, 1, 4>(A, B, args, lda, ldb, stream);
+    }
+  }
   if (cg == 2) {
     if (bn == 256) return launch_major<KIND, 256, EPI, 2>(b_nk, A, B, args, lda, ldb, stream);
     return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs are built for 256-wide tiles only");
@@ -745,6 +771,17 @@ int set_wait_test(long long lose_kb, unsigned long long budget_ns) {
   if (lose_kb < -1 || lose_kb > (1 << 20)) return fail(B200_ERR_BAD_ARGUMENT, "wait test: k-block out of range");
   g_lose_kb = int(lose_kb);
   g_wait_budget_ns = budget_ns ? budget_ns : kWaitBudgetNs;
+  return B200_OK;
+}
+
+int set_deep_staging(int enabled) {
+  g_deep_staging = enabled != 0;
+  return B200_OK;
+}
+
+int set_l2_hints(int hints) {
+  if (hints < -1 || hints > 7) return fail(B200_ERR_BAD_ARGUMENT, "L2 hints: -1 (automatic) or a bit set 0..7");
+  g_l2_hints = hints;
   return B200_OK;
 }
 
@@ -834,6 +871,7 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   args.single_pass = (kind == KIND_TF32 && g_tf32_single_pass_call) ? 1 : 0;
   args.wait_budget_ns = g_wait_budget_ns;
   args.lose_kb = g_lose_kb;
+  args.l2_hints = g_l2_hints >= 0 ? g_l2_hints : 0;
 
   int sms = 0;
   int rc = sm_count_of_current_device(&sms);
@@ -971,12 +1009,27 @@ int launch_sgemm_tf32(const float* A, const float* B, float* C, int64_t M, int64
   return rc;
 }
 
+extern int g_x3_path;
+bool x3_on_chip_applies(const float* A, const float* B, int64_t lda, int64_t ldb);
+int launch_sgemm_3xtf32_on_chip(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                                int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream,
+                                const Tail& tail);
+
 int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                         int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream, const Tail& tail) {
   if (!A || !B || !C) return fail(B200_ERR_BAD_ARGUMENT, "null matrix pointer");
   if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
   if (lda < K || ldb < (b_is_nk ? K : N) || ldc < N)
     return fail(B200_ERR_BAD_ARGUMENT, "a leading dimension is smaller than the row it spans");
+  // Small and medium products are bound by the per-k-block hand-shake between TMA and the MMA lane,
+  // not by the tensor pipe: they take the kernel that splits the operands on chip (one hand-shake
+  // per k-block instead of three, no scratch, one launch).  Large ones keep the split planes in
+  // global memory and run on CTA pairs (measured: 1024^3 36.8 against 48.7 us, 2048^3 176 against
+  // 148 us), except for very long sums: the pair kernel adds a whole K into one accumulator, whose
+  // truncation error grows with K (9.6e-6 at K = 4096), while the on-chip kernel sums K in ranges.
+  if (g_x3_path != 1 && x3_on_chip_applies(A, B, lda, ldb) &&
+      (g_x3_path == 2 || M * N < int64_t(2048) * 2048 || K > 4096))
+    return launch_sgemm_3xtf32_on_chip(A, B, C, M, N, K, lda, ldb, ldc, b_is_nk, stream, tail);
   // The split planes live for this call only: taken from the stream-ordered pool on `stream` and
   // given back on `stream` right behind the GEMM, so calls on different streams (or from different
   // host threads) never share scratch, and nothing is freed while a kernel may still read it.
@@ -996,6 +1049,324 @@ int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int
   const cudaError_t fe = cudaFreeAsync(mem, stream);  // stream-ordered: released after the kernels above
   if (rc == B200_OK && fe != cudaSuccess) rc = fail(B200_ERR_CUDA, "cudaFreeAsync: %s", cudaGetErrorString(fe));
   return rc;
+}
+
+}  // namespace b200
+
+// ------------------------------------------------------------------------------ 3xTF32, operands split on chip
+//
+// The same three-product fp32 GEMM without split planes in global memory.  TMA brings the fp32
+// tiles of A and B into a ring of "raw" stages; four converter warps cut every element in place to
+// its tf32 high part (the top 19 bits) and write the remainder, rounded to tf32, into one of two
+// "low" buffers; the MMA lane then issues lo*hi, hi*lo and hi*hi for the k-block into one TMEM
+// accumulator.  A k-block therefore crosses the TMA -> MMA hand-shake once instead of three times
+// and nothing but A, B and C touches global memory, which is what small and medium products
+// (bound by that hand-shake, not by the tensor pipe) need.  One tile of 128 x BN per CTA, no
+// persistence; C is written from registers (128 contiguous bytes per thread and chunk).
+//   warp 0 producer, warp 1 MMA + tensor memory, warps 2-5 epilogue, warps 6-9 converters.
+namespace b200 {
+namespace {
+
+constexpr int kX3Threads = 320;
+
+template <int BN>
+struct X3Tile {
+  static constexpr int BK = 32;                       // floats of K per stage: one 128-byte swizzle row
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // one stage of fp32 tiles; the low buffers have the same shape
+  static constexpr int SPAN = 32;                      // floats of N in one 128-byte span of an N-contiguous B
+  static constexpr int NSPANS = BN / SPAN;
+  static constexpr int SPAN_BYTES = BK * 128;
+  static constexpr int UNITS = (kSmemBudget - 2048) / RAW_BYTES;  // buffers of RAW_BYTES that fit
+  static constexpr int LO_BUFS = UNITS >= 9 ? 4 : 3;               // ring of low-part buffers
+  static constexpr int STAGES = UNITS - LO_BUFS;                   // ring of raw stages
+  // Tensor memory holds 512 / BN accumulators: number 0 takes the two small products of every
+  // k-block, the others each take hi*hi over one contiguous range of K.  The tensor cores add into
+  // an fp32 accumulator by truncation, so the error of one long chain grows in proportion to K;
+  // short chains summed with correctly rounded additions in the epilogue keep it K-independent.
+  static constexpr int NACC = 512 / BN;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int SMEM_BYTES = (STAGES + LO_BUFS) * RAW_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  static_assert(STAGES >= 3, "the raw ring is too short");
+};
+
+template <int BN, bool B_NK>
+__global__ void __launch_bounds__(kX3Threads, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const GemmArgs p) {
+  using T = X3Tile<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* lo_base = smem + T::STAGES * T::RAW_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(lo_base + T::LO_BUFS * T::RAW_BYTES);
+  uint64_t* full_bar = bars;                        // [STAGES] TMA -> converters, MMA
+  uint64_t* empty_bar = bars + T::STAGES;           // [STAGES] MMA -> producer
+  uint64_t* lo_full = bars + 2 * T::STAGES;         // [LO_BUFS] converters -> MMA
+  uint64_t* lo_empty = lo_full + T::LO_BUFS;        // [LO_BUFS] MMA -> converters
+  uint64_t* acc_full = lo_empty + T::LO_BUFS;       // [1] MMA -> epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.K + T::BK - 1) / T::BK;
+  int mb, nb;
+  tile_coords(int(blockIdx.x), p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+  const int m0 = mb * BM, n0 = nb * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int j = 0; j < T::LO_BUFS; ++j) {
+      mbar_init(&lo_full[j], 128);  // every converter thread arrives
+      mbar_init(&lo_empty[j], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, T::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.wait_budget_ns)) break;
+        uint8_t* sa = smem + stage * T::RAW_BYTES;
+        uint8_t* sb = sa + T::A_BYTES;
+        mbar_arrive_expect_tx(&full_bar[stage], T::RAW_BYTES);
+        tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * T::BK, m0);
+        if constexpr (B_NK) {
+          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * T::BK, n0);
+        } else {
+#pragma unroll
+          for (int sp = 0; sp < T::NSPANS; ++sp)
+            tma_load_2d(sb + sp * T::SPAN_BYTES, &tmap_b, &full_bar[stage], n0 + sp * T::SPAN, kb * T::BK);
+        }
+        if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_instr_desc(KIND_TF32, BM, BN, 0, B_NK ? 0 : 1);
+      const uint32_t ring = smem_u32(smem);
+      const uint32_t lo_ring = smem_u32(lo_base);
+      auto a_desc_at = [](uint32_t base) { return make_smem_desc_sw128(base, 16, 1024); };
+      auto b_desc_at = [](uint32_t base) {
+        return B_NK ? make_smem_desc_sw128(base, 16, 1024) : make_smem_desc(base, T::SPAN_BYTES, 512, 1);
+      };
+      int stage = 0, j = 0;
+      uint32_t phase = 0, lo_phase = 0;
+      bool ok = true;
+      const int big_ranges = min(T::NACC - 1, num_kb);  // accumulators 1 .. big_ranges take hi*hi
+      uint32_t started = 0;                             // bit a: accumulator a has been written
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.wait_budget_ns)) { ok = false; break; }
+        if (!mbar_wait_bounded(&lo_full[j], lo_phase, abort_flag, p.wait_budget_ns)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint64_t a_hi = a_desc_at(ring + stage * T::RAW_BYTES);
+        const uint64_t b_hi = b_desc_at(ring + stage * T::RAW_BYTES + T::A_BYTES);
+        const uint64_t a_lo = a_desc_at(lo_ring + j * T::RAW_BYTES);
+        const uint64_t b_lo = b_desc_at(lo_ring + j * T::RAW_BYTES + T::A_BYTES);
+        const int big = 1 + (kb * big_ranges) / num_kb;
+#pragma unroll
+        for (int prod = 0; prod < 3; ++prod) {  // lo*hi, hi*lo into accumulator 0; hi*hi into its range's
+          const uint64_t ad = prod == 0 ? a_lo : a_hi;
+          const uint64_t bd = prod == 1 ? b_lo : b_hi;
+          const int acc = prod == 2 ? big : 0;
+          const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {  // 8 floats (32 bytes) of K per instruction
+            const uint64_t a_adv = uint64_t((q * 32) >> 4);
+            const uint64_t b_adv = B_NK ? uint64_t((q * 32) >> 4) : uint64_t((q * 8 * 128) >> 4);
+            umma<KIND_TF32>(d_tmem, ad + a_adv, bd + b_adv, idesc, (started >> acc) & 1u);
+            started |= 1u << acc;
+          }
+        }
+        umma_commit(&empty_bar[stage]);
+        umma_commit(&lo_empty[j]);
+        if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
+        if (++j == T::LO_BUFS) { j = 0; lo_phase ^= 1u; }
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ converters
+    const int ct = int(threadIdx.x) - 6 * 32;  // 0..127
+    constexpr int CHUNKS = T::RAW_BYTES / 16;
+    int stage = 0, j = 0;
+    uint32_t phase = 0, lo_phase = 0;
+    for (int kb = 0; kb < num_kb; ++kb) {
+      if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.wait_budget_ns)) break;
+      if (!mbar_wait_bounded(&lo_empty[j], lo_phase ^ 1u, abort_flag, p.wait_budget_ns)) break;
+      uint4* raw = reinterpret_cast<uint4*>(smem + stage * T::RAW_BYTES);
+      uint4* lo = reinterpret_cast<uint4*>(lo_base + j * T::RAW_BYTES);
+#pragma unroll 4
+      for (int c = ct; c < CHUNKS; c += 128) {
+        const uint4 x = raw[c];
+        uint4 hi, l;
+        hi.x = x.x & 0xffffe000u; hi.y = x.y & 0xffffe000u; hi.z = x.z & 0xffffe000u; hi.w = x.w & 0xffffe000u;
+        l.x = __float_as_uint(round_to_tf32(__uint_as_float(x.x) - __uint_as_float(hi.x)));
+        l.y = __float_as_uint(round_to_tf32(__uint_as_float(x.y) - __uint_as_float(hi.y)));
+        l.z = __float_as_uint(round_to_tf32(__uint_as_float(x.z) - __uint_as_float(hi.z)));
+        l.w = __float_as_uint(round_to_tf32(__uint_as_float(x.w) - __uint_as_float(hi.w)));
+        raw[c] = hi;
+        lo[c] = l;
+      }
+      fence_proxy_async_smem();  // the tensor cores read these bytes through the async proxy
+      mbar_arrive(&lo_full[j]);
+      if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
+      if (++j == T::LO_BUFS) { j = 0; lo_phase ^= 1u; }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;
+    const int r_in_tile = quarter * 32 + lane;
+    const int row = m0 + r_in_tile;
+    if (mbar_wait_bounded(acc_full, 0u, abort_flag, p.wait_budget_ns)) {
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
+      const int big_ranges = min(T::NACC - 1, num_kb);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int cn0 = n0 + c * 32;
+        if (cn0 >= p.N) break;
+        // hi*hi ranges in ascending K, then the small products: plain fp32 additions, rounded to nearest
+        uint32_t v[32], w[32];
+        tmem_ld_32x32(taddr + uint32_t(BN + c * 32), v);
+        tmem_ld_wait();
+        for (int a = 2; a <= big_ranges + 1; ++a) {
+          uint32_t u[32];
+          tmem_ld_32x32(taddr + uint32_t((a > big_ranges ? 0 : a) * BN + c * 32), u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(u[i]));
+        }
+        pack_chunk<EPI_F32>(p, cn0, v, 0.f, w);
+        if (row < p.M) store_chunk<EPI_F32>(p, row, cn0, w);
+      }
+    }
+  }
+
+  __syncwarp();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicOr(&g_umma_status, 1u);
+    uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+template <int BN, bool B_NK>
+int launch_x3(const float* A, const float* B, GemmArgs args, int64_t lda, int64_t ldb, cudaStream_t stream) {
+  using T = X3Tile<BN>;
+  auto kernel = gemm_tf32x3_kernel<BN, B_NK>;
+  static thread_local int last_dev = -1;
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev != last_dev) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+    if (e != cudaSuccess)
+      return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes of shared memory): %s", T::SMEM_BYTES,
+                  cudaGetErrorString(e));
+    last_dev = dev;
+  }
+  args.tiles_m = (args.M + BM - 1) / BM;
+  args.tiles_n = (args.N + BN - 1) / BN;
+  args.group_m = args.tiles_m;  // m fastest: CTAs that are resident together share columns of B
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, KIND_TF32, A, args.M, args.K, lda, T::BK, BM);
+  if (rc) return rc;
+  if (B_NK)
+    rc = make_map(&mb, KIND_TF32, B, args.N, args.K, ldb, T::BK, BN);
+  else
+    rc = make_map(&mb, KIND_TF32, B, args.K, args.N, ldb, T::SPAN, T::BK, /*chunks32=*/true);
+  if (rc) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(args.tiles_m * args.tiles_n));
+  cfg.blockDim = dim3(kX3Threads);
+  cfg.dynamicSmemBytes = T::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int nattr = 0;
+  if (g_use_pdl) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = nattr;
+  B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, ma, mb, args));
+  return B200_OK;
+}
+
+}  // namespace
+
+int g_x3_path = 0;  // 0 = automatic, 1 = split planes in global memory, 2 = split on chip
+
+int set_x3_path(int path) {
+  if (path < 0 || path > 2) return fail(B200_ERR_BAD_ARGUMENT, "3xTF32 path: 0 (automatic), 1 or 2");
+  g_x3_path = path;
+  return B200_OK;
+}
+
+// The on-chip form needs what TMA needs of fp32 operands: 16-byte aligned bases and row pitches.
+bool x3_on_chip_applies(const float* A, const float* B, int64_t lda, int64_t ldb) {
+  return lda % 4 == 0 && ldb % 4 == 0 && reinterpret_cast<uintptr_t>(A) % 16 == 0 &&
+         reinterpret_cast<uintptr_t>(B) % 16 == 0;
+}
+
+int launch_sgemm_3xtf32_on_chip(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                                int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream,
+                                const Tail& tail) {
+  GemmArgs args;
+  memset(&args, 0, sizeof(args));
+  args.C[0] = C;
+  args.n_dest = 1;
+  args.ldc = ldc;
+  args.M = int(M);
+  args.N = int(N);
+  args.K = int(K);
+  const bool c_aligned16 = (ldc * 4) % 16 == 0 && reinterpret_cast<uintptr_t>(C) % 16 == 0;
+  args.store_mode = c_aligned16 ? STORE_VECTOR : STORE_SCALAR;
+  args.bias = tail.bias;
+  args.tail_flags = tail.flags;
+  args.wait_budget_ns = g_wait_budget_ns;
+  args.lose_kb = -1;
+  int sms = 0;
+  int rc = sm_count_of_current_device(&sms);
+  if (rc) return rc;
+  // Narrow tiles until the grid covers the machine: 128 x 128 when that already gives every SM a
+  // tile, else 128 x 64.
+  const int64_t tiles128 = ((M + BM - 1) / BM) * ((N + 127) / 128);
+  const bool wide = tiles128 >= sms;
+  if (wide)
+    return b_is_nk ? launch_x3<128, true>(A, B, args, lda, ldb, stream) : launch_x3<128, false>(A, B, args, lda, ldb, stream);
+  return b_is_nk ? launch_x3<64, true>(A, B, args, lda, ldb, stream) : launch_x3<64, false>(A, B, args, lda, ldb, stream);
 }
 
 }  // namespace b200

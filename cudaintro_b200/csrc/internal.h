@@ -67,6 +67,17 @@ bool dependent_launch_enabled();
 // is how long a single device-side wait may last.  lose_kb = -1, budget_ns = 0 restores normal operation.
 int set_wait_test(long long lose_kb, unsigned long long budget_ns);
 
+// Which 3xTF32 kernel b200_gemm_f32 / b200_linear take: 0 = automatic, 1 = split planes in global
+// memory (scratch from the stream-ordered pool), 2 = operands split on chip.
+int set_x3_path(int path);
+
+// Several destinations: 1 (default) = four staged output tiles per CTA, 0 = two as for one destination.
+int set_deep_staging(int enabled);
+
+// L2 eviction hints of the tensor-core kernel's TMA traffic: -1 = automatic, else a bit set
+// (1 = keep A's slab, 2 = B streams, 4 = C's stores stream).
+int set_l2_hints(int hints);
+
 // 1 (default) = GEMM kernels are launched with programmatic stream serialisation; 0 = plain launches.
 int set_dependent_launch(int enabled);
 
@@ -79,9 +90,13 @@ int set_tile_policy(int cg, int bn, int group_rows);
 // Reads and clears the device-side wait record of the tensor-core kernels (0 = clean).
 int read_and_clear_umma_status(cudaStream_t stream, uint32_t* out);
 
+// may_split_k: a plain product with few tiles may be cut along K inside clusters (the ranges' sums
+// are added in range order); false keeps the single ascending sum whatever the shape.
 int launch_sgemm_ffma(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                       int64_t lda, int64_t ldb, int64_t ldc, bool b_is_nk, cudaStream_t stream,
-                      const Tail& tail = Tail());
+                      const Tail& tail = Tail(), bool may_split_k = false);
+// -1 = automatic, 0 = never cut K, 2 or 4 = that many ranges for every plain FFMA product.
+int set_ffma_ksplit(int ks);
 
 // 3xTF32: tensor-core fp32 GEMM from split operands (a = hi + lo, three products per term).
 int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,

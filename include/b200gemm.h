@@ -147,7 +147,8 @@ int b200_gemm_w8a8_bf16(const int8_t* A, const int8_t* B, const float* row_scale
 /* Row-major GEMM whose result is written to n_dest (1..8) buffers at once: C_list[g] points at
  * the same [M, N] slab (leading dimension ldc) inside destination g.  Destinations may be this
  * GPU's memory or peer GPUs' memory mapped into this process (b200_ipc_import): the epilogue
- * then sends every finished tile over NVLink while later tiles are still being computed, which
+ * then sends every finished tile over NVLink (peers first, C_list[0] last: pass the local copy
+ * there) while later tiles are still being computed, which
  * is how a row-sharded product places its rows in every rank's copy of C without a separate
  * all-gather.  `what` is B200_I8, B200_F16, B200_BF16 or B200_W8A8 (the scales are read only
  * for B200_W8A8).  Remote copies are complete when the kernel has finished on the writing GPU;
@@ -156,6 +157,11 @@ int b200_gemm_w8a8_bf16(const int8_t* A, const int8_t* B, const float* row_scale
 int b200_gemm_multi(int what, const void* A, const void* B, void* const* C_list, int n_dest,
                     const float* row_scale, const float* col_scale, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
+/* b200_gemm_multi stages four output tiles per CTA for its TMA stores (1, default) or two as the
+ * single-destination kernels do (0); with four a CTA drains a whole accumulator without waiting
+ * for NVLink to take the previous boxes.  For measurements; results do not depend on it. */
+int b200_set_multi_staging(int deep);
 
 /* Device memory that other processes on the same machine can map: allocate, export a 64-byte
  * handle, import a peer's handle (enables peer access on first use), close, free. */
@@ -185,6 +191,26 @@ int b200_set_store_policy(int register_stores);
  * (griddepcontrol.wait) for that predecessor to complete before it touches global memory, so
  * stream order is kept.  0: plain launches.  For measurements; results do not depend on it. */
 int b200_set_dependent_launch(int enabled);
+
+/* Which kernel the 3xTF32 mode of b200_gemm_f32 / b200_linear takes (process-wide; for tests and
+ * measurements): 0 = automatic (by size), 1 = the operands are first split into high / low planes in
+ * a scratch buffer taken from a stream-ordered pool on the call's stream, 2 = the operands are split
+ * on chip inside the GEMM kernel (needs 16-byte aligned A, B and row pitches; otherwise 1 is taken).
+ * Both meet the mode's tolerance; their results differ in the last bits. */
+int b200_set_3xtf32_path(int path);
+
+/* K ranges of the FFMA mode of b200_gemm_f32 (process-wide; for tests and measurements): a plain
+ * product with too few 64 x 64 tiles to fill the GPU is cut along K into 2 or 4 ranges, one CTA of a
+ * thread-block cluster each; every range is summed in ascending k and the range sums are added in
+ * range order, so the result is deterministic and differs from the single ascending sum in rounding
+ * only.  -1 = automatic (by shape), 0 = never, 2 or 4 = always that many.  b200_linear never cuts K. */
+int b200_set_ffma_k_ranges(int ranges);
+
+/* L2 eviction hints on the tensor-core kernel's TMA traffic (process-wide; for measurements;
+ * results do not depend on it): -1 = automatic, else a bit set: 1 = the rows of A that a group of
+ * tiles re-reads are kept in L2 in preference to other data (evict last), 2 = B, which streams
+ * past, is the first to be evicted, 4 = so are the stores of C. */
+int b200_set_l2_hints(int hints);
 
 /* Test hook for the kernels' failure handling (process-wide; not for production use).  Every
  * device-side wait of the tensor-core kernel is bounded: a wait that outlasts its budget makes the

@@ -448,6 +448,74 @@ def test_fp32_3xtf32_any_shape(cb, oracle, device, shape, layout_name):
 TOL_TF32 = 2e-3  # one tf32 product per term: operands cut to 10 mantissa bits
 
 
+@pytest.fixture
+def f32_paths(cb):
+    from cudaintro_b200 import capi
+
+    yield capi.lib.b200_set_3xtf32_path, capi.lib.b200_set_ffma_k_ranges
+    capi.lib.b200_set_3xtf32_path(0)
+    capi.lib.b200_set_ffma_k_ranges(-1)
+
+
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "COL_MAJOR_NN", "ROW_MAJOR_BT"])
+@pytest.mark.parametrize("shape", [(64, 64, 64), (332, 516, 1000), (1024, 1024, 1024), (128, 72, 36), (2048, 1100, 520)])
+def test_fp32_3xtf32_both_kernels(cb, oracle, device, f32_paths, shape, layout_name, path):
+    """The two 3xTF32 kernels (1 = split planes in a scratch buffer, 2 = operands split on chip),
+    each forced, on aligned shapes in all layouts: relative Frobenius error <= 1e-5 against the
+    fp64-accumulated product, and a second launch reproduces the first bit for bit."""
+    import torch
+
+    set_path, _ = f32_paths
+    layout = getattr(cb, layout_name)
+    M, N, K = shape
+    rng = np.random.default_rng(M + 3 * N + 7 * K + layout)
+    sa, sb = storage_shapes(cb, M, N, K, layout)
+    a = rng.uniform(-1, 1, sa).astype(np.float32)
+    b = rng.uniform(-1, 1, sb).astype(np.float32)
+    assert set_path(path) == 0
+    ad, bd = to_dev(a, device), to_dev(b, device)
+    c = cb.gemm_f32(ad, bd, layout, mode=cb.F32_3XTF32)
+    c2 = cb.gemm_f32(ad, bd, layout, mode=cb.F32_3XTF32)
+    cb.check_device()
+    assert torch.equal(c, c2)
+    bt = np.ascontiguousarray(b.T) if layout == cb.ROW_MAJOR_BT else b
+    truth = oracle.gemm_f32(a, bt, M, N, K, oracle.ROW_MAJOR if layout == cb.ROW_MAJOR_BT else layout, acc64=True)
+    assert rel_fro(c.cpu().numpy(), truth) <= TOL_F32
+
+
+@pytest.mark.parametrize("ranges", [0, 2, 4])
+@pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "COL_MAJOR_NN", "ROW_MAJOR_BT"])
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (250, 130, 515), (64, 64, 64), (70, 3, 97)])
+def test_fp32_ffma_k_ranges(cb, oracle, device, f32_paths, shape, layout_name, ranges):
+    """FFMA with K cut into 0 (never), 2 or 4 ranges inside a cluster: <= 1e-5 against the
+    fp64-accumulated product and no further from it than twice the reference loop's own distance;
+    with K uncut the result is the single ascending sum (the oracle's bits when the oracle fuses
+    nothing: compared to 1e-6 here); two launches agree bit for bit."""
+    import torch
+
+    _, set_ranges = f32_paths
+    layout = getattr(cb, layout_name)
+    M, N, K = shape
+    rng = np.random.default_rng(M + 3 * N + 7 * K + layout + ranges)
+    sa, sb = storage_shapes(cb, M, N, K, layout)
+    a = rng.uniform(-1, 1, sa).astype(np.float32)
+    b = rng.uniform(-1, 1, sb).astype(np.float32)
+    assert set_ranges(ranges) == 0
+    ad, bd = to_dev(a, device), to_dev(b, device)
+    c = cb.gemm_f32(ad, bd, layout, mode=cb.F32_FFMA)
+    c2 = cb.gemm_f32(ad, bd, layout, mode=cb.F32_FFMA)
+    cb.check_device()
+    assert torch.equal(c, c2)
+    bt = np.ascontiguousarray(b.T) if layout == cb.ROW_MAJOR_BT else b
+    lay = oracle.ROW_MAJOR if layout == cb.ROW_MAJOR_BT else layout
+    truth = oracle.gemm_f32(a, bt, M, N, K, lay, acc64=True)
+    loop = oracle.gemm_f32(a, bt, M, N, K, lay)
+    err = rel_fro(c.cpu().numpy(), truth)
+    assert err <= TOL_F32
+    assert err <= 2 * rel_fro(loop, truth) + 1e-7
+
+
 @pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "COL_MAJOR_NN", "ROW_MAJOR_BT"])
 @pytest.mark.parametrize("shape", [(64, 64, 64), (332, 516, 1000), (1024, 1024, 1024), (4096, 512, 256)])
 def test_fp32_single_pass_tf32(cb, oracle, device, shape, layout_name):

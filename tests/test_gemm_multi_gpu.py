@@ -79,6 +79,35 @@ def test_store_paths_leave_padding_alone(cb, device, policies, register_stores):
         assert bool((out[:M, N:] == 7.0).all()) and bool((out[M:] == 7.0).all())
 
 
+@pytest.mark.parametrize("tiles", [(0, 0), (1, 256), (1, 128), (2, 256)])
+@pytest.mark.parametrize("deep", [1, 0])
+def test_multi_destination_staging_depths_and_tilings(cb, oracle, device, policies, deep, tiles):
+    """b200_gemm_multi with four (default) and two staged output tiles per CTA, under every tiling it
+    can take: all destinations bit-exact against the oracle (int8 -> int32 has eight boxes per
+    256-wide tile, so the four-deep ring wraps), twice in a row."""
+    import torch
+    from cudaintro_b200 import capi
+
+    set_tiles, _ = policies
+    M, N, K = 520, 784, 640
+    rng = np.random.default_rng(17)
+    a = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    b = rng.integers(-127, 128, (K, N)).astype(np.int8)
+    want = oracle.gemm_i8_i32(a, b, M, N, K)
+    ad, bd = to_dev(a, device), to_dev(b, device)
+    set_tiles(tiles[0], tiles[1], 0)
+    try:
+        assert capi.lib.b200_set_multi_staging(deep) == 0
+        for _ in range(2):
+            outs = [torch.full((M, N), -1, dtype=torch.int32, device=device) for _ in range(5)]
+            capi.gemm_multi(capi.I8, ad, bd, [o.data_ptr() for o in outs], M, N, K)
+            cb.check_device()
+            for o in outs:
+                assert np.array_equal(o.cpu().numpy(), want)
+    finally:
+        capi.lib.b200_set_multi_staging(1)
+
+
 @pytest.mark.parametrize("register_stores", [False, True])
 def test_multi_destination_gemm_on_one_gpu(cb, oracle, device, policies, register_stores):
     import torch

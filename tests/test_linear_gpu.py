@@ -100,8 +100,14 @@ def test_linear_equals_product_then_bias_then_relu_as_separate_steps(cb, device)
     x = torch.randn((300, 1024), device=device, generator=g)
     w = torch.randn((640, 1024), device=device, generator=g) * 0.05
     b = torch.rand(640, device=device, generator=g) - 0.5
+    from cudaintro_b200 import capi
+
     fused = cb.linear(x, w, b, cb.ROW_MAJOR_BT, relu=True)
-    steps = torch.relu(cb.gemm_f32(x, w, cb.ROW_MAJOR_BT, mode=cb.F32_FFMA) + b)
+    capi.lib.b200_set_ffma_k_ranges(0)  # the layer keeps one ascending sum per output; make the plain product do so too
+    try:
+        steps = torch.relu(cb.gemm_f32(x, w, cb.ROW_MAJOR_BT, mode=cb.F32_FFMA) + b)
+    finally:
+        capi.lib.b200_set_ffma_k_ranges(-1)
     assert torch.equal(fused, steps)
     xb, wb = x.bfloat16(), w.bfloat16()
     fused = cb.linear(xb, wb, b, cb.ROW_MAJOR_BT, relu=True)
