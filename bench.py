@@ -379,7 +379,7 @@ def timed_ms(fn, steps, barrier, warmup=3):
     return e0.elapsed_time(e1) / steps
 
 
-def w8a8_sharded_record(world, rank, device, steps, barrier, max_over_ranks):
+def w8a8_sharded_record(world, rank, device, steps, barrier, max_over_ranks, multicast=False):
     """The row-sharded W8A8 linear (M=8192, N=28672, K=8192, bf16 out, C complete on every rank) on
     the GPUs of this run, whatever the main workload is: fused step, GEMM phase alone, NCCL
     all-gather alone, and the one-GPU time of the whole product measured on rank 0 in the same run,
@@ -411,7 +411,8 @@ def w8a8_sharded_record(world, rank, device, steps, barrier, max_over_ranks):
                     "eff_compute": 1.0, "eff_e2e": 1.0})
         return rec
 
-    fused = FusedShardedGemm(M, N, torch.bfloat16, device)
+    fused = FusedShardedGemm(M, N, torch.bfloat16, device, multicast=multicast)
+    rec["gather"] = "nvls (multimem.st to a multicast mapping)" if multicast else "fused (one TMA store per rank)"
 
     def fused_step():
         fused.step(capi.W8A8, a, b, extra["row_scale"], extra["col_scale"])
@@ -471,16 +472,15 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-w8a8-record", action="store_true", help="skip the sharded W8A8 side record")
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
-                    help="N>1: fused = the GEMM epilogue stores each tile into every rank's C over NVLink; "
-                         "nccl = GEMM, then NCCL all-gather")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nvls", "nccl"],
+                    help="N>1: fused = the GEMM epilogue stores each tile into every rank's C over NVLink (one TMA "
+                         "store per rank); nvls = it writes each tile once with multimem.st to a multicast mapping "
+                         "of C (replicated in the NVSwitch); nccl = GEMM, then NCCL all-gather")
     ap.add_argument("--clock-sampling", default="rank0", choices=["rank0", "off"],
                     help="rank0: a separate nvidia-smi process polls rank 0's GPU; off: no clock record")
     ap.add_argument("--multi-tile", default="", metavar="CG,BN",
                     help="force the tiling of every GEMM of the run (CTA grouping, tile width), e.g. 1,128; "
                          "for measurements of the multi-destination epilogue")
-    ap.add_argument("--multi-staging", type=int, default=4, choices=[2, 4],
-                    help="output tiles staged per CTA by the multi-destination epilogue (4 = default of the library)")
     ap.add_argument("--register-stores", action="store_true",
                     help="write C straight from registers instead of staged TMA stores (for comparison)")
     args = ap.parse_args()
@@ -512,8 +512,6 @@ def main():
     kind, M, N, K, in_b, out_b, unit = WORKLOADS[args.workload]
     if args.register_stores:
         capi.set_store_policy(True)
-    if args.multi_staging != 4:
-        capi._check(capi.lib.b200_set_multi_staging(0))
     if args.multi_tile:
         cg_, bn_ = (int(x) for x in args.multi_tile.split(","))
         cb.set_tile_policy(cg_, bn_, 0)
@@ -534,10 +532,10 @@ def main():
 
     fused = None
     step = nccl_step
-    if world > 1 and args.gather == "fused":
+    if world > 1 and args.gather in ("fused", "nvls"):
         from cudaintro_b200.sharded import FusedShardedGemm
 
-        fused = FusedShardedGemm(M, N, out_dtype(kind), device)
+        fused = FusedShardedGemm(M, N, out_dtype(kind), device, multicast=(args.gather == "nvls"))
         what = {"bf16": capi.BF16, "f16": capi.F16, "i8": capi.I8, "w8a8": capi.W8A8}[kind]
 
         def step():
@@ -700,7 +698,8 @@ def main():
             w8a8_rec = None  # the main line already is that measurement
         else:
             torch.cuda.empty_cache()
-            w8a8_rec = w8a8_sharded_record(world, rank, device, min(args.steps, 20), barrier, max_over_ranks)
+            w8a8_rec = w8a8_sharded_record(world, rank, device, min(args.steps, 20), barrier, max_over_ranks,
+                                           multicast=(args.gather == "nvls"))
 
     if rank != 0:
         if world > 1:
@@ -733,7 +732,9 @@ def main():
         "dtype": {"bf16": "bf16", "f16": "f16", "i8": "int8", "w8a8": "int8"}[kind], "data": "synthetic",
         "config": {"workload": args.workload, "M": M, "N": N, "K": K, "layout": "row-major",
                    "parallelism": f"rows of A over {world} GPU(s), B replicated" + (
-                       "" if world == 1 else (", tiles stored into every rank's C by the GEMM epilogue (peer stores over NVLink)"
+                       "" if world == 1 else ((", tiles written once by the GEMM epilogue to a multicast mapping of C "
+                                               "(multimem.st, replicated in the NVSwitch)") if args.gather == "nvls" else
+                                              ", tiles stored into every rank's C by the GEMM epilogue (peer stores over NVLink)"
                                               if fused_in_step else ", NCCL all-gather of C")),
                    "l2": "inputs larger than L2 (no flush needed)" if (M_local * K + K * N) * in_b > 126e6
                          else "inputs fit L2: back-to-back launches re-use it"},

@@ -49,11 +49,11 @@ SIGNATURES = {
     "b200_set_dependent_launch": (_int, [_int]),
     "b200_test_lose_arrival": (_int, [_i64, C.c_uint64]),
     "b200_set_l2_hints": (_int, [_int]),
-    "b200_set_multi_staging": (_int, [_int]),
     "b200_set_3xtf32_path": (_int, [_int]),
     "b200_set_ffma_k_ranges": (_int, [_int]),
     "b200_gemm_multi": (_int, [_int, _p, _p, C.POINTER(C.c_void_p), _int, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                _p]),
+    "b200_gemm_multicast": (_int, [_int, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p]),
     "b200_peer_marker": (_int, [C.POINTER(C.c_void_p), _int, _int, C.c_uint32, _p]),
     "b200_peer_alloc": (_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "b200_peer_free": (_int, [_p]),
@@ -310,6 +310,17 @@ class HostWeights:
 def set_store_policy(register_stores: bool = False) -> None:
     """True: C is written straight from registers; False: automatic (staged TMA stores when aligned)."""
     _check(lib.b200_set_store_policy(1 if register_stores else 0))
+
+
+def gemm_multicast(what: int, a, b, mc_ptr: int, M: int, N: int, K: int, row_scale=None, col_scale=None) -> None:
+    """Row-major GEMM written once to the multicast address `mc_ptr` of the [M, N] slab (every GPU bound
+    to the multicast object receives it).  `what` is I8, F16, BF16 or W8A8."""
+    import torch
+
+    with torch.cuda.device(a.device):
+        _check(lib.b200_gemm_multicast(what, a.data_ptr(), b.data_ptr(), C.c_void_p(int(mc_ptr)),
+                                       0 if row_scale is None else row_scale.data_ptr(),
+                                       0 if col_scale is None else col_scale.data_ptr(), M, N, K, 0, 0, 0, _stream()))
 
 
 def gemm_multi(what: int, a, b, dest_ptrs, M: int, N: int, K: int, row_scale=None, col_scale=None) -> None:

@@ -502,7 +502,6 @@ extern "C" int b200_gemm_host_weights(const void* weights, const void* A, void* 
 extern "C" int b200_set_store_policy(int register_stores) { return set_store_policy(register_stores); }
 extern "C" int b200_set_dependent_launch(int enabled) { return set_dependent_launch(enabled); }
 extern "C" int b200_set_l2_hints(int hints) { return set_l2_hints(hints); }
-extern "C" int b200_set_multi_staging(int deep) { return set_deep_staging(deep); }
 extern "C" int b200_set_3xtf32_path(int path) { return set_x3_path(path); }
 extern "C" int b200_set_ffma_k_ranges(int ranges) { return set_ffma_ksplit(ranges); }
 extern "C" int b200_test_lose_arrival(int64_t k_block, uint64_t wait_budget_ns) {
@@ -526,6 +525,26 @@ extern "C" int b200_gemm_multi(int what, const void* A, const void* B, void* con
   }
   return launch_umma_gemm_multi(kind, epi, A, B, C_list, n_dest, M, N, K, lda, ldb, ldc, false, row_scale,
                                 col_scale, 0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_gemm_multicast(int what, const void* A, const void* B, void* C_multicast, const float* row_scale,
+                                   const float* col_scale, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                   int64_t ldc, void* stream) {
+  if (!C_multicast) return fail(B200_ERR_BAD_ARGUMENT, "null multicast pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ERR_BAD_ARGUMENT, "M, N and K must be positive");
+  if (lda == 0) lda = K;
+  if (ldb == 0) ldb = N;
+  if (ldc == 0) ldc = N;
+  int kind, epi;
+  switch (what) {
+    case B200_I8: kind = KIND_I8; epi = EPI_I32; break;
+    case B200_F16: kind = KIND_F16; epi = EPI_F16; break;
+    case B200_BF16: kind = KIND_BF16; epi = EPI_BF16; break;
+    case B200_W8A8: kind = KIND_I8; epi = EPI_W8A8_BF16; break;
+    default: return fail(B200_ERR_BAD_ARGUMENT, "b200_gemm_multicast: unsupported type %d", what);
+  }
+  return launch_umma_gemm_multicast(kind, epi, A, B, C_multicast, M, N, K, lda, ldb, ldc, row_scale, col_scale,
+                                    static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200_peer_alloc(size_t bytes, void** ptr) {

@@ -50,15 +50,11 @@ constexpr int kThreads = 192;    // producer warp, MMA warp, four epilogue warps
 constexpr int kSmemBudget = 227 * 1024;
 
 bool g_use_pdl = true;  // launch the GEMM kernel with programmatic stream serialisation
-bool g_deep_staging = true;  // several destinations: stage four output tiles instead of two
 
 // CG = 1: one CTA owns a 128 x BN tile.  CG = 2: a pair of CTAs (cluster of 2) owns a 256 x BN tile;
 // each CTA stages its own 128 rows of A and its own BN/2 columns of B, and the even-ranked CTA
 // issues tcgen05.mma.cta_group::2 for both.
-// NSTG = output tiles (128 rows x 128 bytes) staged for the TMA stores: 2 for one destination; 4 when
-// every tile goes to several GPUs, so that a CTA can drain a whole accumulator without waiting for
-// NVLink to take the previous boxes (the ring gives up one stage for it).
-template <int KIND, int BN_, int CG_ = 1, int NSTG_ = 2>
+template <int KIND, int BN_, int CG_ = 1>
 struct Tile {
   static constexpr int ELEM = KIND == KIND_I8 ? 1 : (KIND == KIND_TF32 ? 4 : 2);
   static constexpr int BN = BN_;
@@ -72,8 +68,8 @@ struct Tile {
   static constexpr int B_BYTES = BN_CTA * 128;
   static constexpr int SPAN_BYTES = BK * 128;  // one span of B: BK k-rows of 128 bytes
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int NSTG = NSTG_;
-  static constexpr int STAGING_BYTES = NSTG * BM * 128;  // 128-row x 128-byte output tiles for the TMA stores
+  static constexpr int NSTG = 2;
+  static constexpr int STAGING_BYTES = NSTG * BM * 128;  // two 128-row x 128-byte output tiles for the TMA stores
   static constexpr int STAGES_FIT = (kSmemBudget - 2048 - STAGING_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // BN is a power of two here
@@ -82,7 +78,9 @@ struct Tile {
 
 constexpr int kMaxDest = 8;  // copies of C one launch can write (this GPU's and up to 7 peers')
 
-enum StoreMode { STORE_SCALAR = 0, STORE_VECTOR = 1, STORE_TMA = 2 };
+// STORE_MULTIMEM: tiles are staged like for STORE_TMA, then written with multimem.st to a multicast
+// address (one store reaches every GPU bound to the multicast object, replicated in the NVSwitch).
+enum StoreMode { STORE_SCALAR = 0, STORE_VECTOR = 1, STORE_TMA = 2, STORE_MULTIMEM = 3 };
 
 struct CMaps {
   CUtensorMap m[kMaxDest];
@@ -208,16 +206,17 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, 
   }
 }
 
-template <int KIND, int BN, bool B_NK, int EPI, int CG, int NSTG>
+template <int KIND, int BN, bool B_NK, int EPI, int CG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CMaps tmap_c, const GemmArgs p) {
-  using T = Tile<KIND, BN, CG, NSTG>;
+  using T = Tile<KIND, BN, CG>;
   constexpr int TILE_M = BM * CG;
+  constexpr int NSTG = T::NSTG;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes: align the stage ring to that.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* staging = smem + T::STAGES * T::STAGE_BYTES;  // NSTG output tiles, 128 rows x 128 bytes each
+  uint8_t* staging = smem + T::STAGES * T::STAGE_BYTES;  // two output tiles, 128 rows x 128 bytes each
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + T::STAGING_BYTES);
   uint64_t* full_bar = bars;                   // [STAGES] producer(s) -> MMA   (pair: the leader's is used)
   uint64_t* empty_bar = bars + T::STAGES;      // [STAGES] MMA -> producer      (pair: one in each CTA)
@@ -434,7 +433,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       float rs = 0.f;
       if constexpr (EPI == EPI_W8A8_BF16) rs = row < p.M ? __ldg(p.row_scale + row) : 0.f;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(ab * BN);
-      if (p.store_mode == STORE_TMA) {
+      if (p.store_mode >= STORE_TMA) {
         // Stage 128 x 128-byte output tiles in shared memory (swizzled like the tensor map expects)
         // and let TMA write them: whole rows per request, clipped at the edges of C, one request
         // per destination buffer.
@@ -443,7 +442,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int n0 = nb * BN + bx * BOX_COLS;
           if (n0 >= p.N) break;  // uniform across the four warps
           uint8_t* buf = staging + (boxes % uint32_t(NSTG)) * (BM * 128);
-          if (store_thread) tma_store_wait_read<NSTG - 1>();  // the stores that last used `buf` have read it
+          if (store_thread && p.store_mode == STORE_TMA) tma_store_wait_read<NSTG - 1>();  // the stores that last used `buf` have read it
           named_barrier_sync(1, kEpiThreads);
 #pragma unroll
           for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
@@ -457,6 +456,26 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               *reinterpret_cast<uint4*>(buf + r_in_tile * 128 + ((unit ^ (r_in_tile & 7)) << 4)) =
                   make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
             }
+          }
+          if (p.store_mode == STORE_MULTIMEM) {
+            // All four warps write the staged tile to the multicast address: eight consecutive lanes
+            // take the eight 16-byte units of one row (128 contiguous bytes per row in every copy).
+            // A tile two boxes back used this buffer; every thread finished reading it before it
+            // arrived at the barrier of the box in between.
+            named_barrier_sync(1, kEpiThreads);
+            constexpr int ELEMS_PER_UNIT = 16 / OUT_BYTES;
+            char* mc = static_cast<char*>(p.C[0]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int u = i * kEpiThreads + (quarter * 32 + lane);
+              const int r = u >> 3, unit = u & 7;
+              const uint4 val = *reinterpret_cast<const uint4*>(buf + r * 128 + ((unit ^ (r & 7)) << 4));
+              const int grow = tile_row0 + r, gcol = n0 + unit * ELEMS_PER_UNIT;
+              if (grow < p.M && gcol + ELEMS_PER_UNIT <= p.N)
+                multimem_st_v4(mc + (int64_t(grow) * p.ldc + gcol) * OUT_BYTES, val);
+            }
+            ++boxes;
+            continue;
           }
           fence_proxy_async_smem();
           named_barrier_sync(1, kEpiThreads);
@@ -497,7 +516,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         else mbar_arrive(&acc_empty[ab]);
       }
     }
-    if (store_thread) tma_store_wait_all<0>();  // every output tile has left for global memory
+    if (store_thread && p.store_mode == STORE_TMA) tma_store_wait_all<0>();  // every output tile has left for global memory
   }
 
   // Every role gets here: either its loop ended or its wait was abandoned.
@@ -591,11 +610,11 @@ int sm_count_of_current_device(int* out) {
   return B200_OK;
 }
 
-template <int KIND, int BN, bool B_NK, int EPI, int CG, int NSTG = 2>
+template <int KIND, int BN, bool B_NK, int EPI, int CG>
 int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb,
                cudaStream_t stream) {
-  using T = Tile<KIND, BN, CG, NSTG>;
-  auto kernel = gemm_umma_kernel<KIND, BN, B_NK, EPI, CG, NSTG>;
+  using T = Tile<KIND, BN, CG>;
+  auto kernel = gemm_umma_kernel<KIND, BN, B_NK, EPI, CG>;
   // The shared-memory attribute is per device: set it whenever this thread meets a new device.
   static thread_local int last_dev = -1;
   int dev = 0;
@@ -680,6 +699,7 @@ int g_force_store = 0;                                  // 0 = automatic, STORE_
 unsigned long long g_wait_budget_ns = kWaitBudgetNs;    // per-wait limit handed to the kernels
 int g_lose_kb = -1;                                     // give-up test: k-block whose arrival is left out
 int g_l2_hints = -1;                                    // -1 = automatic, else the bit set of GemmArgs::l2_hints
+thread_local bool g_multicast_call = false;              // set by launch_umma_gemm_multicast around its launch
 thread_local bool g_tf32_single_pass_call = false;      // set by launch_sgemm_tf32 around its launch
 
 // Stream-ordered memory pool for per-call scratch (the split planes of the 3xTF32 product), one per
@@ -718,14 +738,6 @@ int launch_bn(int bn, int cg, bool b_nk, const void* A, const void* B, GemmArgs 
   args.tiles_m = int((args.M + BM * cg - 1) / (BM * cg));
   args.group_m = (g_group_rows ? g_group_rows : kDefaultGroupRows) / (BM * cg);
   if (args.group_m < 1) args.group_m = 1;
-  // Several destinations (row-major B, the multi-GPU entry point): four staged output tiles.
-  if constexpr (EPI != EPI_F32) {
-    if (args.n_dest > 1 && !b_nk && args.store_mode == STORE_TMA && g_deep_staging) {
-      if (cg == 2 && bn == 256) return launch_one<KIND, 256, false, EPI, 2, 4>(A, B, args, lda, ldb, stream);
-      if (cg == 1 && bn == 256) return launch_one<KIND, 256, false, EPI, 1, 4>(A, B, args, lda, ldb, stream);
-      if (cg == 1 && bn == 128) return launch_one<KIND, 128, false, EPI, 1, 4>(A, B, args, lda, ldb, stream);
-    }
-  }
   if (cg == 2) {
     if (bn == 256) return launch_major<KIND, 256, EPI, 2>(b_nk, A, B, args, lda, ldb, stream);
     return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs are built for 256-wide tiles only");
@@ -774,11 +786,6 @@ int set_wait_test(long long lose_kb, unsigned long long budget_ns) {
   return B200_OK;
 }
 
-int set_deep_staging(int enabled) {
-  g_deep_staging = enabled != 0;
-  return B200_OK;
-}
-
 int set_l2_hints(int hints) {
   if (hints < -1 || hints > 7) return fail(B200_ERR_BAD_ARGUMENT, "L2 hints: -1 (automatic) or a bit set 0..7");
   g_l2_hints = hints;
@@ -815,6 +822,17 @@ int launch_umma_gemm(int kind, int epi, const void* A, const void* B, void* C, i
   void* one[1] = {C};
   return launch_umma_gemm_multi(kind, epi, A, B, one, 1, M, N, K, lda, ldb, ldc, b_is_nk, row_scale, col_scale,
                                 force_bn, stream, tail);
+}
+
+int launch_umma_gemm_multicast(int kind, int epi, const void* A, const void* B, void* C_multicast, int64_t M, int64_t N,
+                               int64_t K, int64_t lda, int64_t ldb, int64_t ldc, const float* row_scale,
+                               const float* col_scale, cudaStream_t stream) {
+  void* one[1] = {C_multicast};
+  g_multicast_call = true;
+  const int rc = launch_umma_gemm_multi(kind, epi, A, B, one, 1, M, N, K, lda, ldb, ldc, false, row_scale, col_scale, 0,
+                                        stream, Tail());
+  g_multicast_call = false;
+  return rc;
 }
 
 int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void* const* C_list, int n_dest,
@@ -864,6 +882,12 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
   args.tiles_n = 0;
   // Aligned C: staged TMA stores (or 16-byte register stores when forced); otherwise element by element.
   args.store_mode = !c_aligned16 ? STORE_SCALAR : (g_force_store == STORE_VECTOR ? STORE_VECTOR : STORE_TMA);
+  if (g_multicast_call) {
+    // the destination is a multicast address: only multimem instructions may touch it
+    if (!c_aligned16 || (N * out_elem) % 16)
+      return fail(B200_ERR_UNSUPPORTED, "a multicast destination needs 16-byte aligned rows of C (N and ldc)");
+    args.store_mode = STORE_MULTIMEM;
+  }
   args.row_scale = row_scale;
   args.col_scale = col_scale;
   args.bias = tail.bias;
@@ -1024,11 +1048,12 @@ int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int
   // Small and medium products are bound by the per-k-block hand-shake between TMA and the MMA lane,
   // not by the tensor pipe: they take the kernel that splits the operands on chip (one hand-shake
   // per k-block instead of three, no scratch, one launch).  Large ones keep the split planes in
-  // global memory and run on CTA pairs (measured: 1024^3 36.8 against 48.7 us, 2048^3 176 against
-  // 148 us), except for very long sums: the pair kernel adds a whole K into one accumulator, whose
-  // truncation error grows with K (9.6e-6 at K = 4096), while the on-chip kernel sums K in ranges.
+  // global memory and run on CTA pairs (measured on chip / split planes: 1024^3 29.7 / 48.4 us,
+  // 2048^3 127 / 145 us, 4096^3 901 / 743 us), except for very long sums: the pair kernel adds a
+  // whole K into one accumulator, whose truncation error grows with K (9.6e-6 at K = 4096), while
+  // the on-chip kernel sums K in ranges (4.9e-6 there).
   if (g_x3_path != 1 && x3_on_chip_applies(A, B, lda, ldb) &&
-      (g_x3_path == 2 || M * N < int64_t(2048) * 2048 || K > 4096))
+      (g_x3_path == 2 || M * N <= int64_t(2048) * 2048 || K > 4096))
     return launch_sgemm_3xtf32_on_chip(A, B, C, M, N, K, lda, ldb, ldc, b_is_nk, stream, tail);
   // The split planes live for this call only: taken from the stream-ordered pool on `stream` and
   // given back on `stream` right behind the GEMM, so calls on different streams (or from different
@@ -1056,13 +1081,19 @@ int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int
 // ------------------------------------------------------------------------------ 3xTF32, operands split on chip
 //
 // The same three-product fp32 GEMM without split planes in global memory.  TMA brings the fp32
-// tiles of A and B into a ring of "raw" stages; four converter warps cut every element in place to
-// its tf32 high part (the top 19 bits) and write the remainder, rounded to tf32, into one of two
-// "low" buffers; the MMA lane then issues lo*hi, hi*lo and hi*hi for the k-block into one TMEM
-// accumulator.  A k-block therefore crosses the TMA -> MMA hand-shake once instead of three times
-// and nothing but A, B and C touches global memory, which is what small and medium products
-// (bound by that hand-shake, not by the tensor pipe) need.  One tile of 128 x BN per CTA, no
-// persistence; C is written from registers (128 contiguous bytes per thread and chunk).
+// tiles of A and B into a ring of "raw" stages.  Four converter warps split them: every thread owns
+// one row of the A tile, reads its 32 floats from the stage and writes the tf32 high parts (top 19
+// bits) and the remainders, rounded to tf32, into tensor memory, where the MMA takes its A operand
+// from; B is cut to its high part in place and its remainder goes to one of two small shared-memory
+// buffers.  The MMA lane then issues lo*hi, hi*lo and hi*hi for the k-block.  Against the
+// split-plane form a k-block crosses the TMA -> MMA hand-shake once instead of three times, nothing
+// but A, B and C touches global memory, and the tensor cores read only B from shared memory (a tf32
+// operand is four bytes per element, and shared-memory bandwidth is what bounds a tf32 main loop).
+// Tensor memory also holds several accumulators: number 0 takes the two small products of every
+// k-block, the others each take hi*hi over one contiguous range of K.  The tensor cores add into
+// an fp32 accumulator by truncation, so the error of one long chain grows in proportion to K;
+// short chains added with correctly rounded fp32 additions in the epilogue keep it small.
+// One tile of 128 x BN per CTA, no persistence; C is written from registers.
 //   warp 0 producer, warp 1 MMA + tensor memory, warps 2-5 epilogue, warps 6-9 converters.
 namespace b200 {
 namespace {
@@ -1074,21 +1105,19 @@ struct X3Tile {
   static constexpr int BK = 32;                       // floats of K per stage: one 128-byte swizzle row
   static constexpr int A_BYTES = BM * 128;
   static constexpr int B_BYTES = BN * 128;
-  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // one stage of fp32 tiles; the low buffers have the same shape
+  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;  // one stage of fp32 tiles
   static constexpr int SPAN = 32;                      // floats of N in one 128-byte span of an N-contiguous B
   static constexpr int NSPANS = BN / SPAN;
   static constexpr int SPAN_BYTES = BK * 128;
-  static constexpr int UNITS = (kSmemBudget - 2048) / RAW_BYTES;  // buffers of RAW_BYTES that fit
-  static constexpr int LO_BUFS = UNITS >= 9 ? 4 : 3;               // ring of low-part buffers
-  static constexpr int STAGES = UNITS - LO_BUFS;                   // ring of raw stages
-  // Tensor memory holds 512 / BN accumulators: number 0 takes the two small products of every
-  // k-block, the others each take hi*hi over one contiguous range of K.  The tensor cores add into
-  // an fp32 accumulator by truncation, so the error of one long chain grows in proportion to K;
-  // short chains summed with correctly rounded additions in the epilogue keep it K-independent.
-  static constexpr int NACC = 512 / BN;
+  static constexpr int LO_BUFS = 2;                    // low parts of B (shared memory) and both parts of A (tensor memory)
+  static constexpr int STAGES_FIT = (kSmemBudget - 2048 - LO_BUFS * B_BYTES) / RAW_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  // Tensor memory, 512 columns: [0, 128) two A buffers of 32 high + 32 low columns; then NACC accumulators.
+  static constexpr int A_COLS = LO_BUFS * 2 * BK;
+  static constexpr int NACC = (512 - A_COLS) / BN;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int SMEM_BYTES = (STAGES + LO_BUFS) * RAW_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
-  static_assert(STAGES >= 3, "the raw ring is too short");
+  static constexpr int SMEM_BYTES = STAGES * RAW_BYTES + LO_BUFS * B_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  static_assert(STAGES >= 3 && NACC >= 2, "ring or accumulator budget too small");
 };
 
 template <int BN, bool B_NK>
@@ -1098,12 +1127,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   using T = X3Tile<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* lo_base = smem + T::STAGES * T::RAW_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(lo_base + T::LO_BUFS * T::RAW_BYTES);
-  uint64_t* full_bar = bars;                        // [STAGES] TMA -> converters, MMA
+  uint8_t* lo_base = smem + T::STAGES * T::RAW_BYTES;  // LO_BUFS buffers of B_BYTES: low parts of B
+  uint64_t* bars = reinterpret_cast<uint64_t*>(lo_base + T::LO_BUFS * T::B_BYTES);
+  uint64_t* full_bar = bars;                        // [STAGES] TMA -> converters
   uint64_t* empty_bar = bars + T::STAGES;           // [STAGES] MMA -> producer
-  uint64_t* lo_full = bars + 2 * T::STAGES;         // [LO_BUFS] converters -> MMA
-  uint64_t* lo_empty = lo_full + T::LO_BUFS;        // [LO_BUFS] MMA -> converters
+  uint64_t* lo_full = bars + 2 * T::STAGES;         // [LO_BUFS] converters -> MMA: the k-block is split
+  uint64_t* lo_empty = lo_full + T::LO_BUFS;        // [LO_BUFS] MMA -> converters: its buffers are free again
   uint64_t* acc_full = lo_empty + T::LO_BUFS;       // [1] MMA -> epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -1138,6 +1167,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t acc_base = tmem_base + uint32_t(T::A_COLS);
 
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -1169,41 +1199,39 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       constexpr uint32_t idesc = make_instr_desc(KIND_TF32, BM, BN, 0, B_NK ? 0 : 1);
       const uint32_t ring = smem_u32(smem);
       const uint32_t lo_ring = smem_u32(lo_base);
-      auto a_desc_at = [](uint32_t base) { return make_smem_desc_sw128(base, 16, 1024); };
       auto b_desc_at = [](uint32_t base) {
         return B_NK ? make_smem_desc_sw128(base, 16, 1024) : make_smem_desc(base, T::SPAN_BYTES, 512, 1);
       };
       int stage = 0, j = 0;
-      uint32_t phase = 0, lo_phase = 0;
+      uint32_t lo_phase = 0;
       bool ok = true;
       const int big_ranges = min(T::NACC - 1, num_kb);  // accumulators 1 .. big_ranges take hi*hi
       uint32_t started = 0;                             // bit a: accumulator a has been written
       for (int kb = 0; kb < num_kb && ok; ++kb) {
-        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.wait_budget_ns)) { ok = false; break; }
+        // the converters waited for the stage themselves; their arrival covers it
         if (!mbar_wait_bounded(&lo_full[j], lo_phase, abort_flag, p.wait_budget_ns)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint64_t a_hi = a_desc_at(ring + stage * T::RAW_BYTES);
         const uint64_t b_hi = b_desc_at(ring + stage * T::RAW_BYTES + T::A_BYTES);
-        const uint64_t a_lo = a_desc_at(lo_ring + j * T::RAW_BYTES);
-        const uint64_t b_lo = b_desc_at(lo_ring + j * T::RAW_BYTES + T::A_BYTES);
+        const uint64_t b_lo = b_desc_at(lo_ring + j * T::B_BYTES);
+        const uint32_t a_hi = tmem_base + uint32_t(j * 2 * T::BK);  // 32 columns of high parts, then 32 of low parts
+        const uint32_t a_lo = a_hi + uint32_t(T::BK);
         const int big = 1 + (kb * big_ranges) / num_kb;
 #pragma unroll
         for (int prod = 0; prod < 3; ++prod) {  // lo*hi, hi*lo into accumulator 0; hi*hi into its range's
-          const uint64_t ad = prod == 0 ? a_lo : a_hi;
+          const uint32_t at = prod == 0 ? a_lo : a_hi;
           const uint64_t bd = prod == 1 ? b_lo : b_hi;
           const int acc = prod == 2 ? big : 0;
-          const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+          const uint32_t d_tmem = acc_base + uint32_t(acc * BN);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {  // 8 floats (32 bytes) of K per instruction
-            const uint64_t a_adv = uint64_t((q * 32) >> 4);
+          for (int q = 0; q < 4; ++q) {  // 8 floats of K per instruction: 8 columns of A, 32 bytes of B's K
             const uint64_t b_adv = B_NK ? uint64_t((q * 32) >> 4) : uint64_t((q * 8 * 128) >> 4);
-            umma<KIND_TF32>(d_tmem, ad + a_adv, bd + b_adv, idesc, (started >> acc) & 1u);
+            umma_tf32_a_in_tmem(d_tmem, at + uint32_t(q * 8), bd + b_adv, idesc, (started >> acc) & 1u);
             started |= 1u << acc;
           }
         }
         umma_commit(&empty_bar[stage]);
         umma_commit(&lo_empty[j]);
-        if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
+        if (++stage == T::STAGES) stage = 0;
         if (++j == T::LO_BUFS) { j = 0; lo_phase ^= 1u; }
       }
       if (ok) umma_commit(acc_full);
@@ -1211,27 +1239,52 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ converters
     const int ct = int(threadIdx.x) - 6 * 32;  // 0..127
-    constexpr int CHUNKS = T::RAW_BYTES / 16;
+    const int quarter = warp & 3;              // the tensor-memory lanes this warp may touch
+    const int r = quarter * 32 + lane;         // row of the A tile this thread splits
+    constexpr int B_CHUNKS = T::B_BYTES / 16;
     int stage = 0, j = 0;
     uint32_t phase = 0, lo_phase = 0;
     for (int kb = 0; kb < num_kb; ++kb) {
-      if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.wait_budget_ns)) break;
-      if (!mbar_wait_bounded(&lo_empty[j], lo_phase ^ 1u, abort_flag, p.wait_budget_ns)) break;
-      uint4* raw = reinterpret_cast<uint4*>(smem + stage * T::RAW_BYTES);
-      uint4* lo = reinterpret_cast<uint4*>(lo_base + j * T::RAW_BYTES);
-#pragma unroll 4
-      for (int c = ct; c < CHUNKS; c += 128) {
-        const uint4 x = raw[c];
-        uint4 hi, l;
-        hi.x = x.x & 0xffffe000u; hi.y = x.y & 0xffffe000u; hi.z = x.z & 0xffffe000u; hi.w = x.w & 0xffffe000u;
-        l.x = __float_as_uint(round_to_tf32(__uint_as_float(x.x) - __uint_as_float(hi.x)));
-        l.y = __float_as_uint(round_to_tf32(__uint_as_float(x.y) - __uint_as_float(hi.y)));
-        l.z = __float_as_uint(round_to_tf32(__uint_as_float(x.z) - __uint_as_float(hi.z)));
-        l.w = __float_as_uint(round_to_tf32(__uint_as_float(x.w) - __uint_as_float(hi.w)));
-        raw[c] = hi;
-        lo[c] = l;
+      bool ok = mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.wait_budget_ns) &&
+                mbar_wait_bounded(&lo_empty[j], lo_phase ^ 1u, abort_flag, p.wait_budget_ns);
+      ok = __all_sync(0xffffffffu, ok) != 0;  // the warp stays together for the aligned tensor-memory stores
+      if (!ok) break;
+      tc_fence_after_sync();
+      // A: this thread's row, 8 swizzled 16-byte chunks -> 32 high and 32 low words in tensor memory
+      const uint8_t* arow = smem + stage * T::RAW_BYTES + r * 128;
+      uint32_t hi[32], lo[32];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 x = *reinterpret_cast<const uint4*>(arow + ((c ^ (r & 7)) << 4));
+        const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t h = xs[e] & 0xffffe000u;
+          hi[4 * c + e] = h;
+          lo[4 * c + e] = __float_as_uint(round_to_tf32(__uint_as_float(xs[e]) - __uint_as_float(h)));
+        }
       }
-      fence_proxy_async_smem();  // the tensor cores read these bytes through the async proxy
+      const uint32_t a_t = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(j * 2 * T::BK);
+      tmem_st_32x32(a_t, hi);
+      tmem_st_32x32(a_t + uint32_t(T::BK), lo);
+      // B: element-wise on the stage's bytes, whatever their layout: high parts in place, low parts aside
+      uint4* braw = reinterpret_cast<uint4*>(smem + stage * T::RAW_BYTES + T::A_BYTES);
+      uint4* blo = reinterpret_cast<uint4*>(lo_base + j * T::B_BYTES);
+#pragma unroll 4
+      for (int c = ct; c < B_CHUNKS; c += 128) {
+        const uint4 x = braw[c];
+        uint4 h, l;
+        h.x = x.x & 0xffffe000u; h.y = x.y & 0xffffe000u; h.z = x.z & 0xffffe000u; h.w = x.w & 0xffffe000u;
+        l.x = __float_as_uint(round_to_tf32(__uint_as_float(x.x) - __uint_as_float(h.x)));
+        l.y = __float_as_uint(round_to_tf32(__uint_as_float(x.y) - __uint_as_float(h.y)));
+        l.z = __float_as_uint(round_to_tf32(__uint_as_float(x.z) - __uint_as_float(h.z)));
+        l.w = __float_as_uint(round_to_tf32(__uint_as_float(x.w) - __uint_as_float(h.w)));
+        braw[c] = h;
+        blo[c] = l;
+      }
+      tmem_st_wait();             // the tensor-memory stores have landed
+      fence_proxy_async_smem();   // the tensor cores read the shared-memory bytes through the async proxy
+      tc_fence_before_sync();
       mbar_arrive(&lo_full[j]);
       if (++stage == T::STAGES) { stage = 0; phase ^= 1u; }
       if (++j == T::LO_BUFS) { j = 0; lo_phase ^= 1u; }
@@ -1243,7 +1296,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int row = m0 + r_in_tile;
     if (mbar_wait_bounded(acc_full, 0u, abort_flag, p.wait_budget_ns)) {
       tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
+      const uint32_t taddr = acc_base + (uint32_t(quarter * 32) << 16);
       const int big_ranges = min(T::NACC - 1, num_kb);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {

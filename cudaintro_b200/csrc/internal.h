@@ -42,6 +42,12 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
                            const float* row_scale, const float* col_scale, int force_bn, cudaStream_t stream,
                            const Tail& tail = Tail());
 
+// Same product (row-major B) written once to a multicast address: one store per 16 bytes reaches every
+// GPU's copy of C through the NVSwitch.
+int launch_umma_gemm_multicast(int kind, int epi, const void* A, const void* B, void* C_multicast, int64_t M, int64_t N,
+                               int64_t K, int64_t lda, int64_t ldb, int64_t ldc, const float* row_scale,
+                               const float* col_scale, cudaStream_t stream);
+
 // The same kind of product for at most 128 rows of A (fp16, bf16, or int8 with the int32 or the W8A8
 // epilogue): tiles shared by clusters that split K and add their partial sums through distributed
 // shared memory (gemm_skinny.cu).  *used tells whether the
@@ -70,9 +76,6 @@ int set_wait_test(long long lose_kb, unsigned long long budget_ns);
 // Which 3xTF32 kernel b200_gemm_f32 / b200_linear take: 0 = automatic, 1 = split planes in global
 // memory (scratch from the stream-ordered pool), 2 = operands split on chip.
 int set_x3_path(int path);
-
-// Several destinations: 1 (default) = four staged output tiles per CTA, 0 = two as for one destination.
-int set_deep_staging(int enabled);
 
 // L2 eviction hints of the tensor-core kernel's TMA traffic: -1 = automatic, else a bit set
 // (1 = keep A's slab, 2 = B streams, 4 = C's stores stream).

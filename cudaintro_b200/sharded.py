@@ -144,6 +144,32 @@ class PeerBuffer:
             self._local_ptr = None
 
 
+class SymmetricBuffer:
+    """`nbytes` of device memory on every rank from torch's symmetric-memory allocator, mapped by all
+    ranks: ``ptrs[g]`` is rank g's buffer as seen from this process, ``local`` a torch uint8 view of this
+    rank's own, and ``mc_ptr`` a multicast address of the whole group (0 when the GPUs or the driver
+    offer no NVLink multicast): a ``multimem`` store to ``mc_ptr + off`` lands at ``off`` in every
+    rank's buffer.  Same interface as :class:`PeerBuffer`; torch only allocates and maps here."""
+
+    def __init__(self, nbytes: int, device, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        self.dist, self.group = dist, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.nbytes = nbytes
+        self.local = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self._handle = symm.rendezvous(self.local, group if group is not None else dist.group.WORLD)
+        self.ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        self.mc_ptr = int(self._handle.multicast_ptr or 0)
+
+    def close(self):
+        self._handle = None
+        self.local = None
+
+
 class FusedShardedGemm:
     """Row-sharded GEMM whose epilogue writes each finished tile of this rank's slab into EVERY
     rank's copy of C (peer memory mapped with CUDA IPC), so the gather travels over NVLink while
@@ -153,7 +179,10 @@ class FusedShardedGemm:
     slab has landed in its copy of C.
     """
 
-    def __init__(self, M: int, N: int, out_dtype, device, group=None):
+    def __init__(self, M: int, N: int, out_dtype, device, group=None, multicast: bool = False):
+        """multicast=True: C lives in symmetric memory with an NVLink multicast mapping and every tile
+        is written once with ``multimem.st`` (``b200_gemm_multicast``) instead of once per rank; raises
+        RuntimeError where no multicast mapping can be had.  Not for runs in which a rank may leave."""
         import ctypes as C
 
         import torch
@@ -167,7 +196,16 @@ class FusedShardedGemm:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.part = partition_rows(M, self.world, self.rank)
         self.N = N
-        self._c = PeerBuffer(self.part.padded_rows * N * itemsize, device, group)
+        self.multicast = bool(multicast) and self.world > 1
+        if self.multicast:
+            self._c = SymmetricBuffer(self.part.padded_rows * N * itemsize, device, group)
+            if not self._c.mc_ptr:
+                raise RuntimeError("no NVLink multicast mapping is available for this group")
+            from . import capi as _capi
+
+            self._c.capi = _capi
+        else:
+            self._c = PeerBuffer(self.part.padded_rows * N * itemsize, device, group)
         self._flags = PeerBuffer(256, device, group)
         self._flags.local.zero_()
         torch.cuda.synchronize()
@@ -180,6 +218,7 @@ class FusedShardedGemm:
         # from a start that rotates with CTA and tile, and with this ordering the ranks, which run in
         # step with one another, hit different receivers at any moment instead of the same one.
         self.slab_ptrs = [self._c.ptrs[(self.rank + i) % self.world] + slab_offset for i in range(self.world)]
+        self.mc_slab_ptr = self._c.mc_ptr + slab_offset if self.multicast else 0
         r0 = self.rank * self.part.slot_rows
         self.c_slab = self.c_full[r0:r0 + self.part.rows]
         self._flag_ptrs = (C.c_void_p * self.world)(*[C.c_void_p(p) for p in self._flags.ptrs])
@@ -187,7 +226,10 @@ class FusedShardedGemm:
 
     def launch(self, what: int, a, b, row_scale=None, col_scale=None):
         """The multi-destination GEMM alone (no completion marker)."""
-        if self.part.rows > 0:
+        if self.part.rows > 0 and self.multicast:
+            self.capi.gemm_multicast(what, a, b, self.mc_slab_ptr, self.part.rows, self.N, a.shape[1], row_scale,
+                                     col_scale)
+        elif self.part.rows > 0:
             self.capi.gemm_multi(what, a, b, self.slab_ptrs, self.part.rows, self.N, a.shape[1], row_scale, col_scale)
 
     def mark(self):

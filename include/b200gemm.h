@@ -158,10 +158,20 @@ int b200_gemm_multi(int what, const void* A, const void* B, void* const* C_list,
                     const float* row_scale, const float* col_scale, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, void* stream);
 
-/* b200_gemm_multi stages four output tiles per CTA for its TMA stores (1, default) or two as the
- * single-destination kernels do (0); with four a CTA drains a whole accumulator without waiting
- * for NVLink to take the previous boxes.  For measurements; results do not depend on it. */
-int b200_set_multi_staging(int deep);
+/* The same row-major product written ONCE, to a multicast address: C_multicast points at the [M, N]
+ * slab (leading dimension ldc) inside a multicast mapping of C, i.e. a virtual address bound through
+ * an NVLink multicast object to the same buffer on every GPU of the group (cuMulticastCreate /
+ * cuMulticastBindMem, or a framework's symmetric memory: torch's exposes it as multicast_ptr).  The
+ * epilogue stages every tile in shared memory and writes it with multimem.st: each 16 bytes leave
+ * this GPU once and the NVSwitch delivers them to all copies, this GPU's included, so a row-sharded
+ * product fills every rank's C while sending 1/G of what b200_gemm_multi sends.  Needs N and ldc
+ * in whole 16-byte units; the copies are complete when the kernel has finished, and readers on other
+ * GPUs must order themselves after that (b200_peer_marker).  Keep it out of runs in which a rank
+ * may leave: a process that dies while bound to a multicast object disturbs NVLink for the others.
+ * No counterpart in the reference. */
+int b200_gemm_multicast(int what, const void* A, const void* B, void* C_multicast, const float* row_scale,
+                        const float* col_scale, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                        int64_t ldc, void* stream);
 
 /* Device memory that other processes on the same machine can map: allocate, export a 64-byte
  * handle, import a peer's handle (enables peer access on first use), close, free. */

@@ -142,6 +142,9 @@ def test_policy_knobs_and_multi_gpu_entry_points_validate_arguments(cb):
     assert lib.b200_gemm_multi(capi.I8, one, one, dests, 0, None, None, 16, 16, 16, 0, 0, 0, None) == 1
     assert lib.b200_gemm_multi(capi.F32, one, one, dests, 1, None, None, 16, 16, 16, 0, 0, 0, None) == 1
     assert lib.b200_gemm_multi(capi.W8A8, one, one, dests, 1, None, None, 16, 16, 16, 0, 0, 0, None) == 1  # no scales
+    assert lib.b200_gemm_multicast(capi.I8, one, one, None, None, None, 16, 16, 16, 0, 0, 0, None) == 1
+    assert lib.b200_gemm_multicast(capi.F32, one, one, one, None, None, 16, 16, 16, 0, 0, 0, None) == 1
+    assert lib.b200_gemm_multicast(capi.BF16, one, one, one, None, None, 16, 20, 16, 0, 0, 0, None) == 2  # ragged rows
     assert lib.b200_peer_marker(dests, 9, 0, 1, None) == 1
     assert lib.b200_peer_marker(dests, 2, 2, 1, None) == 1
     assert lib.b200_peer_marker(None, 2, 0, 1, None) == 1

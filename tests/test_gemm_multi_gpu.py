@@ -80,11 +80,9 @@ def test_store_paths_leave_padding_alone(cb, device, policies, register_stores):
 
 
 @pytest.mark.parametrize("tiles", [(0, 0), (1, 256), (1, 128), (2, 256)])
-@pytest.mark.parametrize("deep", [1, 0])
-def test_multi_destination_staging_depths_and_tilings(cb, oracle, device, policies, deep, tiles):
-    """b200_gemm_multi with four (default) and two staged output tiles per CTA, under every tiling it
-    can take: all destinations bit-exact against the oracle (int8 -> int32 has eight boxes per
-    256-wide tile, so the four-deep ring wraps), twice in a row."""
+def test_multi_destination_under_every_tiling(cb, oracle, device, policies, tiles):
+    """b200_gemm_multi under every tiling it can take: all destinations (peers first, destination 0
+    last) bit-exact against the oracle, twice in a row."""
     import torch
     from cudaintro_b200 import capi
 
@@ -96,16 +94,12 @@ def test_multi_destination_staging_depths_and_tilings(cb, oracle, device, polici
     want = oracle.gemm_i8_i32(a, b, M, N, K)
     ad, bd = to_dev(a, device), to_dev(b, device)
     set_tiles(tiles[0], tiles[1], 0)
-    try:
-        assert capi.lib.b200_set_multi_staging(deep) == 0
-        for _ in range(2):
-            outs = [torch.full((M, N), -1, dtype=torch.int32, device=device) for _ in range(5)]
-            capi.gemm_multi(capi.I8, ad, bd, [o.data_ptr() for o in outs], M, N, K)
-            cb.check_device()
-            for o in outs:
-                assert np.array_equal(o.cpu().numpy(), want)
-    finally:
-        capi.lib.b200_set_multi_staging(1)
+    for _ in range(2):
+        outs = [torch.full((M, N), -1, dtype=torch.int32, device=device) for _ in range(5)]
+        capi.gemm_multi(capi.I8, ad, bd, [o.data_ptr() for o in outs], M, N, K)
+        cb.check_device()
+        for o in outs:
+            assert np.array_equal(o.cpu().numpy(), want)
 
 
 @pytest.mark.parametrize("register_stores", [False, True])
@@ -271,5 +265,31 @@ def test_fused_gather_on_two_gpus(cb, device, tmp_path):
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                           "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
                          capture_output=True, text=True, env=env, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    assert "rank 0 ok" in res.stdout and "rank 1 ok" in res.stdout
+
+
+_TWO_GPU_MULTICAST_SCRIPT = _TWO_GPU_SCRIPT.replace(
+    "fs = FusedShardedGemm(M, N, torch.bfloat16, dev)",
+    "fs = FusedShardedGemm(M, N, torch.bfloat16, dev, multicast=True)\nassert fs.multicast and fs.mc_slab_ptr")
+
+
+def test_multicast_gather_on_two_gpus(cb, device, tmp_path):
+    """b200_gemm_multicast on real hardware: two ranks, C in symmetric memory with an NVLink multicast
+    mapping, every tile written once with multimem.st and delivered to both copies by the switch.
+    Bit-exact against the oracle on both ranks and equal to GEMM + NCCL all-gather.  No rank leaves
+    in this test (a process that dies while bound to a multicast object disturbs the other GPUs)."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "two_gpu_mc.py"
+    script.write_text(_TWO_GPU_MULTICAST_SCRIPT)
+    env = dict(os.environ, B200_ROOT=ROOT)
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29534", str(script)],
+                         capture_output=True, text=True, env=env, timeout=600)
+    if "no NVLink multicast mapping" in res.stderr:
+        pytest.skip("this machine offers no NVLink multicast")
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     assert "rank 0 ok" in res.stdout and "rank 1 ok" in res.stdout
