@@ -197,8 +197,8 @@ def sharded_rows_parity(kind, c_full, b, extra, M, N, K, world, device):
     """Rank 0, outside any timed region: rows of the assembled C from EVERY rank's slab (first, last
     and one inner row of each) against the CPU oracle.  The other ranks' rows of A are regenerated
     here from their seeds (make_inputs is deterministic per seed and shape).  Bit-exact for the
-    integer kinds; relative Frobenius error within the stated tolerance for bf16 / fp16.  Raises
-    SystemExit on a mismatch; returns a short description otherwise."""
+    integer kinds; relative Frobenius error within the stated tolerance for bf16 / fp16.  Returns
+    (ok, text): a short description, or which rows differed."""
     import numpy as np
     import torch
 
@@ -235,10 +235,10 @@ def sharded_rows_parity(kind, c_full, b, extra, M, N, K, world, device):
             err = float(np.linalg.norm(got.float().numpy().astype(np.float64) - o32) / np.linalg.norm(o32))
             ok = err <= (1e-2 if kind == "bf16" else 2e-3)
         if not ok:
-            raise SystemExit(f"sharded {kind} GEMM: rows {local} of rank {r}'s slab differ from the CPU oracle")
+            return False, f"sharded {kind} GEMM: rows {local} of rank {r}'s slab differ from the CPU oracle"
         checked += len(local)
         del a_r, extra_r
-    return f"oracle rows ok ({checked} rows from {world} slab(s), every rank's among them)"
+    return True, f"oracle rows ok ({checked} rows from {world} slab(s), every rank's among them)"
 
 
 # ----------------------------------------------------------------------------- CPU legs
@@ -360,6 +360,38 @@ def reference_arm(args, wl_name):
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------------------------------------- failing together
+
+_CLEANUPS = []  # callables that release peer-mapped / multicast-bound memory, newest last
+
+
+def agree(ok, message, world, device):
+    """Every rank calls this with its own verdict.  If any rank's check failed, ALL ranks release their
+    peer-mapped and multicast-bound buffers in the same order, leave the process group and exit 1
+    together: no rank is killed from outside while its memory is still bound to an NVLink multicast
+    object or mapped by a peer."""
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([1 if ok else 0], device=device, dtype=torch.int32)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if int(t.item()) == 1:
+        return
+    if not ok:
+        print(message, file=sys.stderr, flush=True)
+    torch.cuda.synchronize()
+    for fn in reversed(_CLEANUPS):
+        try:
+            fn()
+        except Exception as e:  # keep releasing the rest
+            print(f"cleanup: {e!r}", file=sys.stderr, flush=True)
+    _CLEANUPS.clear()
+    if world > 1:
+        dist.destroy_process_group()
+    sys.exit(1)
+
+
 # ----------------------------------------------------------------------------- the sharded W8A8 configuration
 
 def timed_ms(fn, steps, barrier, warmup=3):
@@ -404,7 +436,8 @@ def w8a8_sharded_record(world, rank, device, steps, barrier, max_over_ranks, mul
     if world == 1:
         gemm_only()
         cb.check_device()
-        rec["parity"] = sharded_rows_parity(kind, sharded.result(), b, extra, M, N, K, 1, device)
+        ok, rec["parity"] = sharded_rows_parity(kind, sharded.result(), b, extra, M, N, K, 1, device)
+        agree(ok, rec["parity"], 1, device)
         t1 = timed_ms(gemm_only, steps, barrier)
         cb.check_device()
         rec.update({"one_gpu_ms": t1, "step_ms": t1, "gemm_phase_ms": t1, "value": ops / (t1 * 1e-3) / 1e12,
@@ -412,6 +445,7 @@ def w8a8_sharded_record(world, rank, device, steps, barrier, max_over_ranks, mul
         return rec
 
     fused = FusedShardedGemm(M, N, torch.bfloat16, device, multicast=multicast)
+    _CLEANUPS.append(fused.close)
     rec["gather"] = "nvls (multimem.st to a multicast mapping)" if multicast else "fused (one TMA store per rank)"
 
     def fused_step():
@@ -421,11 +455,12 @@ def w8a8_sharded_record(world, rank, device, steps, barrier, max_over_ranks, mul
     fused_step()
     cb.check_device()
     barrier()
-    if not torch.equal(fused.result().view(torch.int16), sharded.result().view(torch.int16)):
-        raise SystemExit(f"rank {rank}: W8A8 fused GEMM + all-gather differs from GEMM + NCCL all-gather")
+    agree(torch.equal(fused.result().view(torch.int16), sharded.result().view(torch.int16)),
+          f"rank {rank}: W8A8 fused GEMM + all-gather differs from GEMM + NCCL all-gather", world, device)
+    ok = True
     if rank == 0:
-        rec["parity"] = sharded_rows_parity(kind, fused.result(), b, extra, M, N, K, world, device)
-    barrier()
+        ok, rec["parity"] = sharded_rows_parity(kind, fused.result(), b, extra, M, N, K, world, device)
+    agree(ok, rec.get("parity", ""), world, device)
     step_ms = timed_ms(fused_step, steps, barrier)
     cb.check_device()
     barrier()
@@ -456,6 +491,7 @@ def w8a8_sharded_record(world, rank, device, steps, barrier, max_over_ranks, mul
         "note": "step = multi-destination GEMM (every tile stored into every rank's C over NVLink) + completion "
                 "marker; every GPU receives (G-1)/G of C; eff_* against the one-GPU time of the same run"})
     fused.close()
+    _CLEANUPS.remove(fused.close)
     return rec
 
 
@@ -472,8 +508,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-w8a8-record", action="store_true", help="skip the sharded W8A8 side record")
-    ap.add_argument("--gather", default="fused", choices=["fused", "nvls", "nccl"],
-                    help="N>1: fused = the GEMM epilogue stores each tile into every rank's C over NVLink (one TMA "
+    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nvls", "nccl"],
+                    help="N>1: auto = nvls for bf16 / fp16 outputs where the machine has NVLink multicast, else fused; fused = the GEMM epilogue stores each tile into every rank's C over NVLink (one TMA "
                          "store per rank); nvls = it writes each tile once with multimem.st to a multicast mapping "
                          "of C (replicated in the NVSwitch); nccl = GEMM, then NCCL all-gather")
     ap.add_argument("--clock-sampling", default="rank0", choices=["rank0", "off"],
@@ -530,12 +566,30 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # How C is completed on every rank.  auto: for 16-bit outputs of 16-bit products the epilogue writes each
+    # tile once to a multicast mapping (fewer bytes leave the GPU; measured faster at 2, 4 and 8 GPUs), where the
+    # machine offers one; store-heavy products (int32 or W8A8 outputs) are bound by what every GPU must take
+    # in, which the multicast's loop-back copy only adds to, so they store once per rank with TMA.
+    gather = args.gather
+    if gather == "auto":
+        gather = "nvls" if (world > 1 and kind in ("bf16", "f16")) else "fused"
     fused = None
     step = nccl_step
-    if world > 1 and args.gather in ("fused", "nvls"):
+    if world > 1 and gather in ("fused", "nvls"):
         from cudaintro_b200.sharded import FusedShardedGemm
 
-        fused = FusedShardedGemm(M, N, out_dtype(kind), device, multicast=(args.gather == "nvls"))
+        if gather == "nvls":
+            try:
+                fused = FusedShardedGemm(M, N, out_dtype(kind), device, multicast=True)
+            except RuntimeError as e:  # no multicast on this machine: the same on every rank
+                if args.gather == "nvls":
+                    raise
+                if rank == 0:
+                    print(f"multicast gather not available ({e}); using per-rank TMA stores", file=sys.stderr)
+                gather = "fused"
+        if fused is None:
+            fused = FusedShardedGemm(M, N, out_dtype(kind), device)
+        _CLEANUPS.append(fused.close)
         what = {"bf16": capi.BF16, "f16": capi.F16, "i8": capi.I8, "w8a8": capi.W8A8}[kind]
 
         def step():
@@ -545,18 +599,17 @@ def main():
         nccl_step()
         step()
         barrier()
-        if not torch.equal(fused.result().view(torch.uint8), sharded.result().view(torch.uint8)):
-            raise SystemExit(f"rank {rank}: fused GEMM + all-gather differs from GEMM + NCCL all-gather")
+        agree(torch.equal(fused.result().view(torch.uint8), sharded.result().view(torch.uint8)),
+              f"rank {rank}: fused GEMM + all-gather differs from GEMM + NCCL all-gather", world, device)
 
     # untimed check of the assembled C against the CPU oracle: rows from every rank's slab
-    parity = None
-    if True:
-        if fused is None:
-            nccl_step()
-            barrier()
-        if rank == 0:
-            parity = sharded_rows_parity(kind, (fused or sharded).result(), b, extra, M, N, K, world, device)
+    if fused is None:
+        nccl_step()
         barrier()
+    ok, parity = True, None
+    if rank == 0:
+        ok, parity = sharded_rows_parity(kind, (fused or sharded).result(), b, extra, M, N, K, world, device)
+    agree(ok, parity or "", world, device)
 
     clocks = ClockSampler(local_rank, enabled=(rank == 0 and args.clock_sampling != "off"))
     for _ in range(max(args.warmup, 3)):
@@ -664,8 +717,7 @@ def main():
         dev_rows = sharded.c_slab[:8].cpu()
         same = torch.equal(hc[:8], dev_rows) if kind == "i8" else bool(
             (hc[:8].float() - dev_rows.float()).norm() <= 1e-2 * dev_rows.float().norm())
-        if not same:
-            raise SystemExit(f"rank {rank}: host-buffer result differs from the device-buffer result")
+        agree(same, f"rank {rank}: host-buffer result differs from the device-buffer result", world, device)
         e2e = {"value": ops_step * e2e_steps / dt / 1e12, "unit": unit,
                "h2d_bytes_per_step": world * M_local * K * in_b, "d2h_bytes_per_step": M * N * out_b,
                "steps": e2e_steps, "ms_per_step": dt / e2e_steps * 1e3,
@@ -693,13 +745,14 @@ def main():
     if not args.no_w8a8_record:
         if fused is not None:
             fused.close()
+            _CLEANUPS.remove(fused.close)
             fused = None
         if args.workload == "w8a8" and world == 1:
             w8a8_rec = None  # the main line already is that measurement
         else:
             torch.cuda.empty_cache()
             w8a8_rec = w8a8_sharded_record(world, rank, device, min(args.steps, 20), barrier, max_over_ranks,
-                                           multicast=(args.gather == "nvls"))
+                                           multicast=(args.gather == "nvls"))  # auto: per-rank TMA stores
 
     if rank != 0:
         if world > 1:
@@ -733,7 +786,7 @@ def main():
         "config": {"workload": args.workload, "M": M, "N": N, "K": K, "layout": "row-major",
                    "parallelism": f"rows of A over {world} GPU(s), B replicated" + (
                        "" if world == 1 else ((", tiles written once by the GEMM epilogue to a multicast mapping of C "
-                                               "(multimem.st, replicated in the NVSwitch)") if args.gather == "nvls" else
+                                               "(multimem.st, replicated in the NVSwitch)") if gather == "nvls" else
                                               ", tiles stored into every rank's C by the GEMM epilogue (peer stores over NVLink)"
                                               if fused_in_step else ", NCCL all-gather of C")),
                    "l2": "inputs larger than L2 (no flush needed)" if (M_local * K + K * N) * in_b > 126e6
@@ -752,6 +805,9 @@ def main():
     if w8a8_rec is not None:
         line["w8a8_sharded"] = w8a8_rec
     if world > 1:
+        line["gather"] = {"nvls": "multimem.st from the GEMM epilogue to a multicast mapping of C",
+                          "fused": "one TMA store per rank from the GEMM epilogue (peer memory)",
+                          "nccl": "GEMM, then NCCL all-gather"}[gather]
         line["gemm_phase"] = {"ms": gemm_ms, "value": ops_step / (gemm_ms * 1e-3) / 1e12, "unit": unit,
                               "note": "all ranks' GEMMs without the all-gather"}
         if fused_in_step:
