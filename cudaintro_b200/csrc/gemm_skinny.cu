@@ -49,6 +49,22 @@ namespace {
 
 __device__ uint32_t g_skinny_status = 0;  // bit 0: a bounded wait ran out somewhere
 
+// Timeline instrumentation, compiled in only with -DB200_SKINNY_STAMPS (a measurement build; the
+// shipped library has none of it).  Every CTA records %globaltimer for its first 64 k-blocks at four
+// points: the producer lane after its wait for a free stage and after issuing the stage's loads,
+// the MMA lane after its wait for the full stage and after issuing the stage's MMAs; plus one stamp
+// right after the dependency wait.  Layout: stamps[cta][5][64] 64-bit words.
+#ifdef B200_SKINNY_STAMPS
+__device__ unsigned long long* g_sk_stamps = nullptr;
+#define SK_STAMP(which, i)                                                                     \
+  do {                                                                                         \
+    if (g_sk_stamps != nullptr && (i) < 64)                                                    \
+      g_sk_stamps[(size_t(blockIdx.x) * 5 + (which)) * 64 + (i)] = global_timer_ns();          \
+  } while (0)
+#else
+#define SK_STAMP(which, i) do { } while (0)
+#endif
+
 constexpr int kSkThreads = 128;
 constexpr int kSkMaxRows = 128;          // rows of C one launch can produce
 constexpr int kSkMaxStages = 8;
@@ -146,6 +162,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   // no-op without a programmatic dependency) and let the next kernel begin its own set-up.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) SK_STAMP(4, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -154,6 +171,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       uint32_t phase = 0;
       for (int i = 0; i < kb_count; ++i) {
         if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) break;
+        SK_STAMP(0, i);
         uint8_t* sa = smem + stage * stage_bytes;
         uint8_t* sb = sa + a_bytes;
         const int k = (kb0 + i) * bk;
@@ -165,6 +183,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           for (int s = 0; s < nspans; ++s)
             tma_load_2d(sb + s * span_bytes, &tmap_b, &full_bar[stage], n0 + s * span_cols, k);
         }
+        SK_STAMP(1, i);
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -185,6 +204,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       bool ok = true;
       for (int i = 0; i < kb_count; ++i) {
         if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+        SK_STAMP(2, i);
         tc_fence_after_sync();
 #pragma unroll
         for (int j = 0; j < 4; ++j) {  // 32 bytes of K per instruction
@@ -195,6 +215,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                                                 (i | j) != 0 ? 1u : 0u);
         }
         umma_commit(&empty_bar[stage]);
+        SK_STAMP(3, i);
         a_desc += stage_step;
         b_desc += stage_step;
         if (++stage == p.stages) { stage = 0; phase ^= 1u; a_desc = a_desc0; b_desc = b_desc0; }
@@ -377,6 +398,16 @@ int max_resident_clusters(int splits, int* out) {
 }
 
 }  // namespace
+
+#ifdef B200_SKINNY_STAMPS
+}  // namespace b200
+// Measurement build only: where the skinny kernel writes its timeline (device memory, 5 * 64 words per CTA), or null.
+extern "C" int b200_debug_set_skinny_stamps(void* device_buffer) {
+  unsigned long long* p = static_cast<unsigned long long*>(device_buffer);
+  return cudaMemcpyToSymbol(b200::g_sk_stamps, &p, sizeof(p)) == cudaSuccess ? 0 : 3;
+}
+namespace b200 {
+#endif
 
 int read_and_clear_skinny_status(uint32_t* out) {
   uint32_t zero = 0;

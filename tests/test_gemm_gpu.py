@@ -484,6 +484,34 @@ def test_fp32_3xtf32_both_kernels(cb, oracle, device, f32_paths, shape, layout_n
     assert rel_fro(c.cpu().numpy(), truth) <= TOL_F32
 
 
+@pytest.mark.parametrize("path", [1, 2])
+def test_fp32_3xtf32_calls_on_two_streams_do_not_share_scratch(cb, oracle, device, f32_paths, path):
+    """Two 3xTF32 products with different operands, enqueued alternately on two streams so that their
+    kernels overlap on the GPU: each result must be its own product (the split-plane kernel takes its
+    scratch per call from a stream-ordered pool on the call's stream; the on-chip kernel has none)."""
+    import torch
+
+    set_path, _ = f32_paths
+    assert set_path(path) == 0
+    rng = np.random.default_rng(77 + path)
+    shapes = [(512, 384, 1024), (384, 640, 768)]
+    hosts = [(rng.uniform(-1, 1, (M, K)).astype(np.float32), rng.uniform(-1, 1, (K, N)).astype(np.float32))
+             for M, N, K in shapes]
+    devs = [(to_dev(a, device), to_dev(b, device)) for a, b in hosts]
+    outs = [torch.empty((M, N), device=device) for M, N, K in shapes]
+    streams = [torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)]
+    torch.cuda.synchronize()
+    for _ in range(8):
+        for i in (0, 1):
+            with torch.cuda.stream(streams[i]):
+                cb.gemm_f32(devs[i][0], devs[i][1], mode=cb.F32_3XTF32, out=outs[i])
+    for st in streams:
+        st.synchronize()
+    cb.check_device()
+    for (M, N, K), (a, b), out in zip(shapes, hosts, outs):
+        assert rel_fro(out.cpu().numpy(), oracle.gemm_f32(a, b, M, N, K, acc64=True)) <= TOL_F32
+
+
 @pytest.mark.parametrize("ranges", [0, 2, 4])
 @pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "COL_MAJOR_NN", "ROW_MAJOR_BT"])
 @pytest.mark.parametrize("shape", [(1024, 1024, 1024), (250, 130, 515), (64, 64, 64), (70, 3, 97)])
