@@ -2,6 +2,8 @@
 
     python -m cudaintro_b200.build            # build if sources are newer than the library
     python -m cudaintro_b200.build --force
+    python -m cudaintro_b200.build --stamps   # measurement build: libb200gemm_stamps.so, whose skinny kernel
+                                              # records a per-k-block timeline (see cudaintro_b200/timeline.py)
 
 The library is a plain C-ABI shared object (see ``include/b200gemm.h``); nothing in it links
 against Python or torch.  Objects are compiled in parallel, one nvcc per source file.
@@ -80,5 +82,33 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+STAMPS_LIB = os.path.join(PKG, "libb200gemm_stamps.so")
+
+
+def build_stamps() -> str:
+    """The same sources with -DB200_SKINNY_STAMPS, into a library of its own (never loaded by the package)."""
+    obj_dir = os.path.join(PKG, "build", "stamps")
+    os.makedirs(obj_dir, exist_ok=True)
+
+    def compile_one(src: str) -> str:
+        obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
+        cmd = [_nvcc(), *NVCC_FLAGS, "-DB200_SKINNY_STAMPS", "-c", os.path.join(CSRC, src), "-o", obj]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n{res.stdout}\n{res.stderr}")
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as pool:
+        objs = list(pool.map(compile_one, SOURCES))
+    res = subprocess.run([_nvcc(), "-shared", "-o", STAMPS_LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
+                          "-cudart", "shared"], capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    return STAMPS_LIB
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--stamps" in sys.argv:
+        print(build_stamps())
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

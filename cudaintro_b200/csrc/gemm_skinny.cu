@@ -53,13 +53,15 @@ __device__ uint32_t g_skinny_status = 0;  // bit 0: a bounded wait ran out somew
 // shipped library has none of it).  Every CTA records %globaltimer for its first 64 k-blocks at four
 // points: the producer lane after its wait for a free stage and after issuing the stage's loads,
 // the MMA lane after its wait for the full stage and after issuing the stage's MMAs; plus one stamp
-// right after the dependency wait.  Layout: stamps[cta][5][64] 64-bit words.
+// right after the dependency wait (row 4, word 0); row 5 holds the tail: word 0 = accumulator complete,
+// 1 = tensor memory moved to the exchange slots, 2 = past the barrier, 3 = sums stored (thread 0 each).
+// Layout: stamps[cta][6][64] 64-bit words.
 #ifdef B200_SKINNY_STAMPS
 __device__ unsigned long long* g_sk_stamps = nullptr;
 #define SK_STAMP(which, i)                                                                     \
   do {                                                                                         \
     if (g_sk_stamps != nullptr && (i) < 64)                                                    \
-      g_sk_stamps[(size_t(blockIdx.x) * 5 + (which)) * 64 + (i)] = global_timer_ns();          \
+      g_sk_stamps[(size_t(blockIdx.x) * 6 + (which)) * 64 + (i)] = global_timer_ns();          \
   } while (0)
 #else
 #define SK_STAMP(which, i) do { } while (0)
@@ -232,6 +234,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     // ---------------------------------------------------------------- step 2: tensor memory -> slots
     bool acc_ready = mbar_wait_bounded(acc_full, 0u, abort_flag);
     acc_ready = __all_sync(0xffffffffu, acc_ready) != 0;  // the warp acts as one from here on
+    if (threadIdx.x == 0) SK_STAMP(5, 0);
     tc_fence_after_sync();
     if (acc_ready) {
       const uint32_t quarter = tmem_base + (uint32_t(warp * 32) << 16);  // rows 32 * warp + lane
@@ -261,7 +264,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   }
   // Step 3: every slot is complete and visible to its owner.
   __syncwarp();
+  if (threadIdx.x == 0) SK_STAMP(5, 1);
   if (S > 1) cluster_sync_all(); else __syncthreads();
+  if (threadIdx.x == 0) SK_STAMP(5, 2);
 
   if (*abort_flag == 0u) {
     // ---------------------------------------------------------------- step 4: add, finish, store
@@ -346,6 +351,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 
   // Every role gets here: its loop ended or its wait was given up.
   __syncwarp();
+  if (threadIdx.x == 0) SK_STAMP(5, 3);
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {
