@@ -98,6 +98,114 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a,
                : "memory");
 }
 
+// Step 4 of the kernel below for one epilogue kind: add the K ranges' slots in range order, apply the tail,
+// convert and store.  A thread takes (block of 32 rows, group of 8 columns) pairs: its lane is the row
+// inside the block, so reads of a slot are conflict-free (consecutive lanes, 16 bytes each).  Only four
+// warps run here, one per scheduler, so nothing hides an instruction's latency but the warp's own
+// independent work: four pairs are processed together (their loads, sums and conversions interleave).
+// Taken one at a time, a pair cost 0.87 us (about 1650 clocks of one dependent chain), 2.9 us of a
+// 20 us launch at 16 rows and 11 us at 128.
+template <int EPI>
+__device__ __forceinline__ void skinny_finish(const SkinnyArgs& p, const uint4* __restrict__ slots, int R, int S,
+                                              int own_units, int own_chunks, int row_blocks, int col0, int warp,
+                                              int lane) {
+  constexpr bool kInteger = EPI == EPI_I32 || EPI == EPI_W8A8_BF16;
+  constexpr int kOutBytes = EPI == EPI_I32 ? 4 : 2;
+  constexpr int UNR = 4;
+  const bool relu = (p.tail_flags & B200_LINEAR_RELU) != 0;
+  const int total = row_blocks * own_chunks * 4;
+  const int range_stride = own_units * R;  // uint4 words between the slots of successive K ranges
+  for (int u0 = warp; u0 < total; u0 += 4 * UNR) {
+    uint32_t acc[UNR][8];
+    int row[UNR], nc[UNR], ofs[UNR];
+    bool live[UNR];
+#pragma unroll
+    for (int b = 0; b < UNR; ++b) {
+      const int u = u0 + 4 * b;
+      live[b] = u < total;
+      const int uu = live[b] ? u : u0;  // a dead pair re-reads a live one's slots and stores nothing
+      const int rb = uu % row_blocks, g = uu / row_blocks;
+      row[b] = rb * 32 + lane;
+      nc[b] = col0 + g * 8;
+      ofs[b] = g * 2 * R + row[b];
+      live[b] = live[b] && nc[b] < p.N;
+    }
+#pragma unroll
+    for (int b = 0; b < UNR; ++b) {
+      const uint4 t0 = slots[ofs[b]], t1 = slots[ofs[b] + R];
+      acc[b][0] = t0.x; acc[b][1] = t0.y; acc[b][2] = t0.z; acc[b][3] = t0.w;
+      acc[b][4] = t1.x; acc[b][5] = t1.y; acc[b][6] = t1.z; acc[b][7] = t1.w;
+    }
+    for (int r = 1; r < S; ++r) {
+#pragma unroll
+      for (int b = 0; b < UNR; ++b) {
+        const uint4 t0 = slots[r * range_stride + ofs[b]], t1 = slots[r * range_stride + ofs[b] + R];
+        const uint32_t in[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if constexpr (kInteger) acc[b][j] += in[j];
+          else acc[b][j] = __float_as_uint(__uint_as_float(acc[b][j]) + __uint_as_float(in[j]));
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < UNR; ++b) {
+      uint32_t w[8];  // 8 outputs: 8 words of int32, or 4 words of two 16-bit values
+      if constexpr (EPI == EPI_I32) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = acc[b][j];
+      } else {
+        float rs = 0.0f;
+        if constexpr (EPI == EPI_W8A8_BF16) rs = (live[b] && row[b] < p.M) ? __ldg(p.row_scale + row[b]) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float x0, x1;
+          if constexpr (EPI == EPI_W8A8_BF16) {
+            // (float(acc) * row_scale) * col_scale, each step rounded once, then to bf16
+            const float c0 = __ldg(p.col_scale + min(max(nc[b], 0) + 2 * j, p.N - 1));
+            const float c1 = __ldg(p.col_scale + min(max(nc[b], 0) + 2 * j + 1, p.N - 1));
+            x0 = __fmul_rn(__fmul_rn(__int2float_rn(int(acc[b][2 * j])), rs), c0);
+            x1 = __fmul_rn(__fmul_rn(__int2float_rn(int(acc[b][2 * j + 1])), rs), c1);
+          } else {
+            x0 = __uint_as_float(acc[b][2 * j]);
+            x1 = __uint_as_float(acc[b][2 * j + 1]);
+            if (p.bias != nullptr) {
+              x0 += __ldg(p.bias + min(nc[b] + 2 * j, p.N - 1));
+              x1 += __ldg(p.bias + min(nc[b] + 2 * j + 1, p.N - 1));
+            }
+            if (relu) {
+              x0 = fmaxf(0.0f, x0);
+              x1 = fmaxf(0.0f, x1);
+            }
+          }
+          if constexpr (EPI == EPI_F16) {
+            __half2 h = __floats2half2_rn(x0, x1);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+      }
+      if (live[b] && row[b] < p.M) {
+        char* dst = static_cast<char*>(p.C) + (int64_t(row[b]) * p.ldc + nc[b]) * kOutBytes;
+        if (p.vec_store && nc[b] + 8 <= p.N) {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+          if constexpr (kOutBytes == 4) *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+        } else if constexpr (kOutBytes == 4) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (nc[b] + j < p.N) reinterpret_cast<uint32_t*>(dst)[j] = w[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (nc[b] + j < p.N) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(w[j >> 1] >> ((j & 1) * 16));
+        }
+      }
+    }
+  }
+}
+
 // ESZ (bytes per element of A and B) and B_NK (B given as [N,K]) are template parameters although the
 // code would run with them as arguments: the TMA-issuing lane and the MMA-issuing lane each execute a
 // short serial loop per k-block that paces the whole CTA, and every instruction in those loops shows in
@@ -270,82 +378,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 
   if (*abort_flag == 0u) {
     // ---------------------------------------------------------------- step 4: add, finish, store
-    // A thread takes (block of 32 rows, group of 8 columns) pairs: its lane is the row inside the
-    // block, so reads of a slot are conflict-free (consecutive lanes, 16 bytes each).
-    const bool relu = (p.tail_flags & B200_LINEAR_RELU) != 0;
-    const bool integer = p.kind == KIND_I8;
-    const int out_bytes = p.epi == EPI_I32 ? 4 : 2;
     const int row_blocks = R / 32;
     const int col0 = n0 + int(rank) * own_chunks * 32;  // first column this CTA finishes
     const uint4* slots = reinterpret_cast<const uint4*>(exch);
-    for (int u = warp; u < row_blocks * own_chunks * 4; u += 4) {
-      const int rb = u % row_blocks, g = u / row_blocks;
-      const int row = rb * 32 + lane;
-      const int nc = col0 + g * 8;
-      if (nc >= p.N) continue;
-      uint32_t acc[8];  // int32 sums or fp32 sums, as bits
-      for (int r = 0; r < S; ++r) {
-        const uint4* part = slots + (r * own_units + g * 2) * R + row;
-        const uint4 t0 = part[0], t1 = part[R];
-        const uint32_t in[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (r == 0) acc[j] = in[j];
-          else if (integer) acc[j] += in[j];
-          else acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __uint_as_float(in[j]));
-        }
-      }
-      uint32_t w[8];  // 8 outputs: 8 words of int32, or 4 words of two 16-bit values
-      if (p.epi == EPI_I32) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) w[j] = acc[j];
-      } else {
-        const float rs = (p.epi == EPI_W8A8_BF16 && row < p.M) ? __ldg(p.row_scale + row) : 0.0f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float x0, x1;
-          if (p.epi == EPI_W8A8_BF16) {
-            // (float(acc) * row_scale) * col_scale, each step rounded once, then to bf16
-            const float c0 = __ldg(p.col_scale + min(nc + 2 * j, p.N - 1));
-            const float c1 = __ldg(p.col_scale + min(nc + 2 * j + 1, p.N - 1));
-            x0 = __fmul_rn(__fmul_rn(__int2float_rn(int(acc[2 * j])), rs), c0);
-            x1 = __fmul_rn(__fmul_rn(__int2float_rn(int(acc[2 * j + 1])), rs), c1);
-          } else {
-            x0 = __uint_as_float(acc[2 * j]);
-            x1 = __uint_as_float(acc[2 * j + 1]);
-            if (p.bias != nullptr) {
-              x0 += __ldg(p.bias + min(nc + 2 * j, p.N - 1));
-              x1 += __ldg(p.bias + min(nc + 2 * j + 1, p.N - 1));
-            }
-            if (relu) {
-              x0 = fmaxf(0.0f, x0);
-              x1 = fmaxf(0.0f, x1);
-            }
-          }
-          if (p.epi == EPI_F16) {
-            __half2 h = __floats2half2_rn(x0, x1);
-            w[j] = *reinterpret_cast<uint32_t*>(&h);
-          } else {
-            __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-            w[j] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        }
-      }
-      if (row < p.M) {
-        char* dst = static_cast<char*>(p.C) + (int64_t(row) * p.ldc + nc) * out_bytes;
-        if (p.vec_store && nc + 8 <= p.N) {
-          *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-          if (out_bytes == 4) *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-        } else if (out_bytes == 4) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (nc + j < p.N) reinterpret_cast<uint32_t*>(dst)[j] = w[j];
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (nc + j < p.N) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(w[j >> 1] >> ((j & 1) * 16));
-        }
-      }
+    switch (p.epi) {
+      case EPI_F16: skinny_finish<EPI_F16>(p, slots, R, S, own_units, own_chunks, row_blocks, col0, warp, lane); break;
+      case EPI_BF16: skinny_finish<EPI_BF16>(p, slots, R, S, own_units, own_chunks, row_blocks, col0, warp, lane); break;
+      case EPI_I32: skinny_finish<EPI_I32>(p, slots, R, S, own_units, own_chunks, row_blocks, col0, warp, lane); break;
+      default: skinny_finish<EPI_W8A8_BF16>(p, slots, R, S, own_units, own_chunks, row_blocks, col0, warp, lane); break;
     }
   }
 
@@ -491,12 +531,11 @@ int launch_skinny_gemm(int kind, int epi, const void* A, const void* B, void* C,
     if (force) return fail(B200_ERR_UNSUPPORTED, "no one-wave configuration of the skinny kernel fits N = %lld", (long long)N);
     return B200_OK;
   }
-  // Not worth a different kernel unless every SM streams clearly less than it would in the general one:
-  // 10 % less for up to 64 rows.  With 96 or 128 rows the exchange area leaves a ring of three to five
-  // stages and A is as large as in the general kernel, which then streams faster per SM (M = 128,
-  // [4096 -> 11008]: 26.6 us there, 28.4 us here at 116 instead of 86 CTAs); such products come here
-  // only when the general tiling would leave more than half of the machine idle.
-  if (!force && (rows > 64 ? best_cost * 2 > general_cost : best_cost * 10 > general_cost * 9)) return B200_OK;
+  // Not worth a different kernel unless every SM streams clearly (10 %) less than it would in the general
+  // one.  Measured on [4096 -> 11008] fp16, this kernel / the general one: 16 rows 19.0 / 25 us, 64 rows
+  // 20.2 / 26 us, 96 rows 22.4 / 26.5 us, 128 rows 25.7 / 26.5 us (there the exchange area leaves a ring of
+  // three stages and A is as large as in the general kernel, so little is left of the advantage).
+  if (!force && best_cost * 10 > general_cost * 9) return B200_OK;
 
   if ((lda * esz) % 16 || (ldb * esz) % 16 || reinterpret_cast<uintptr_t>(A) % 16 || reinterpret_cast<uintptr_t>(B) % 16) {
     if (force) return fail(B200_ERR_UNSUPPORTED, "tensor-core GEMM needs 16-byte aligned A and B pointers and leading dimensions");
