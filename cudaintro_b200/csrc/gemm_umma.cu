@@ -147,13 +147,27 @@ __device__ __forceinline__ void pack_chunk(const GemmArgs& p, int n0, const uint
       }
     }
   } else {
+    // W8A8: the chunk's column scales, four per load where the chunk lies inside C and the scales
+    // are 16-byte aligned (every thread of the warp reads the same addresses: one broadcast each).
+    [[maybe_unused]] float cs[W];
+    if constexpr (EPI == EPI_W8A8_BF16) {
+      if (n0 + W <= p.N && (reinterpret_cast<uintptr_t>(p.col_scale + n0) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < W / 4; ++i) {
+          const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.col_scale + n0) + i);
+          cs[4 * i] = c4.x; cs[4 * i + 1] = c4.y; cs[4 * i + 2] = c4.z; cs[4 * i + 3] = c4.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < W; ++i) cs[i] = __ldg(p.col_scale + min(n0 + i, p.N - 1));
+      }
+    }
 #pragma unroll
     for (int i = 0; i < W / 2; ++i) {
       float x0, x1;
       if constexpr (EPI == EPI_W8A8_BF16) {
         // (float(acc) * row_scale) * col_scale, each step rounded once, then to bf16
-        float c0 = __ldg(p.col_scale + min(n0 + 2 * i, p.N - 1));
-        float c1 = __ldg(p.col_scale + min(n0 + 2 * i + 1, p.N - 1));
+        const float c0 = cs[2 * i], c1 = cs[2 * i + 1];
         x0 = __fmul_rn(__fmul_rn(__int2float_rn(int(v[2 * i])), rs), c0);
         x1 = __fmul_rn(__fmul_rn(__int2float_rn(int(v[2 * i + 1])), rs), c1);
       } else {
@@ -434,22 +448,37 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if constexpr (EPI == EPI_W8A8_BF16) rs = row < p.M ? __ldg(p.row_scale + row) : 0.f;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(ab * BN);
       if (p.store_mode >= STORE_TMA) {
-        // Stage 128 x 128-byte output tiles in shared memory (swizzled like the tensor map expects)
-        // and let TMA write them: whole rows per request, clipped at the edges of C, one request
-        // per destination buffer.
+        // Stage 128 x 128-byte output tiles ("boxes") in shared memory, swizzled like the tensor map
+        // expects, and let TMA write them: whole rows per request, clipped at the edges of C, one
+        // request per destination buffer.  Four warps on four schedulers hide no latency for one
+        // another, so the tensor-memory load of box i + 1 is in flight while box i is converted and
+        // staged, and a box costs one barrier: the thread that issues the stores waits, before it
+        // arrives there, until the store of the box before has read its buffer, which is the buffer
+        // the next box will be staged in.
+        const int cols_left = p.N - nb * BN;
+        const int nboxes = min(BN / BOX_COLS, (cols_left + BOX_COLS - 1) / BOX_COLS);
+        uint32_t vn[CHUNKS_PER_BOX][32];
+#pragma unroll
+        for (int h = 0; h < CHUNKS_PER_BOX; ++h) tmem_ld_32x32(taddr + uint32_t(h * 32), vn[h]);
 #pragma unroll 1
-        for (int bx = 0; bx < BN / BOX_COLS; ++bx) {
+        for (int bx = 0; bx < nboxes; ++bx) {
           const int n0 = nb * BN + bx * BOX_COLS;
-          if (n0 >= p.N) break;  // uniform across the four warps
-          uint8_t* buf = staging + (boxes % uint32_t(NSTG)) * (BM * 128);
-          if (store_thread && p.store_mode == STORE_TMA) tma_store_wait_read<NSTG - 1>();  // the stores that last used `buf` have read it
-          named_barrier_sync(1, kEpiThreads);
+          uint8_t* buf = staging + (boxes & 1u) * (BM * 128);
+          uint32_t v[CHUNKS_PER_BOX][32];
+          tmem_ld_wait();
+#pragma unroll
+          for (int h = 0; h < CHUNKS_PER_BOX; ++h)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[h][i] = vn[h][i];
+          if (bx + 1 < nboxes) {
+#pragma unroll
+            for (int h = 0; h < CHUNKS_PER_BOX; ++h)
+              tmem_ld_32x32(taddr + uint32_t((bx + 1) * BOX_COLS + h * 32), vn[h]);
+          }
 #pragma unroll
           for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
-            uint32_t v[32], w[32];
-            tmem_ld_32x32(taddr + uint32_t(bx * BOX_COLS + h * 32), v);
-            tmem_ld_wait();
-            pack_chunk<EPI>(p, n0 + h * 32, v, rs, w);
+            uint32_t w[32];
+            pack_chunk<EPI>(p, n0 + h * 32, v[h], rs, w);
 #pragma unroll
             for (int i = 0; i < UNITS; ++i) {
               const int unit = h * UNITS + i;
@@ -460,8 +489,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (p.store_mode == STORE_MULTIMEM) {
             // All four warps write the staged tile to the multicast address: eight consecutive lanes
             // take the eight 16-byte units of one row (128 contiguous bytes per row in every copy).
-            // A tile two boxes back used this buffer; every thread finished reading it before it
-            // arrived at the barrier of the box in between.
+            // The box after this one is staged in the other buffer, and the one after that in this
+            // buffer again only by threads that have passed the next box's barrier, i.e. after every
+            // thread has finished the reads below.
             named_barrier_sync(1, kEpiThreads);
             constexpr int ELEMS_PER_UNIT = 16 / OUT_BYTES;
             char* mc = static_cast<char*>(p.C[0]);
@@ -478,6 +508,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             continue;
           }
           fence_proxy_async_smem();
+          if (store_thread) tma_store_wait_read<0>();  // the other buffer is free for the next box
           named_barrier_sync(1, kEpiThreads);
           if (store_thread) {
             // Destination 0 (by convention the local copy) goes last; the others (peer GPUs) are
