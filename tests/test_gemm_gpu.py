@@ -812,6 +812,29 @@ def policy(cb):
 POLICY_SHAPES = [(256, 256, 128), (208, 336, 1008), (16, 512, 4112), (1024, 768, 2048), (257, 272, 64)]
 
 
+def test_l2_eviction_hints_do_not_change_results(cb, device):
+    """b200_set_l2_hints only changes the cache policy words that travel with the TMA loads and stores:
+    every setting must give the bits of the default (int8 exact, bf16 identical)."""
+    import torch
+    from cudaintro_b200 import capi
+
+    g = torch.Generator(device=device).manual_seed(3)
+    a = torch.randint(-127, 128, (1024, 768), dtype=torch.int8, device=device, generator=g)
+    b = torch.randint(-127, 128, (768, 1280), dtype=torch.int8, device=device, generator=g)
+    ah, bh = a.bfloat16(), b.bfloat16()
+    want_i, want_h = cb.gemm_i8_i32(a, b), cb.gemm_bf16(ah, bh)
+    assert torch.equal(want_i, cb.gemm_naive(a, b))
+    try:
+        for hints in range(8):
+            assert capi.lib.b200_set_l2_hints(hints) == 0
+            assert torch.equal(cb.gemm_i8_i32(a, b), want_i), hints
+            assert torch.equal(cb.gemm_bf16(ah, bh), want_h), hints
+        cb.check_device()
+        assert capi.lib.b200_set_l2_hints(8) == 1
+    finally:
+        capi.lib.b200_set_l2_hints(-1)
+
+
 def test_kernel_gives_up_a_wait_that_cannot_end_and_the_device_stays_usable(cb, oracle, device, policy):
     """Failure handling of the tensor-core kernel itself, without any fault: the producer of a
     single-CTA launch leaves out the loads of one k-block (b200_test_lose_arrival), so the MMA
