@@ -76,13 +76,16 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
   const bool bias_first = bias != nullptr && (flags & B200_LINEAR_BIAS_FIRST) != 0;
   const bool bias_last = bias != nullptr && !bias_first;
   const bool relu = (flags & B200_LINEAR_RELU) != 0;
-  float acc[TM][TN];
+  // Accumulators in pairs along n: the inner loop issues packed fp32 FMAs (two per instruction, each an
+  // ordinary IEEE fused multiply-add), which halves the issue slots the FMAs take.
+  float2 acc2[TM][TN / 2];
+  auto acc = [&](int i, int j) -> float& { return (j & 1) ? acc2[i][j >> 1].y : acc2[i][j >> 1].x; };
 #pragma unroll
   for (int j = 0; j < TN; ++j) {
     const int n = n0 + (j / 4) * 64 + tx * 4 + (j % 4);
     const float start = (bias_first && n < N) ? __ldg(bias + n) : 0.f;
 #pragma unroll
-    for (int i = 0; i < TM; ++i) acc[i][j] = start;
+    for (int i = 0; i < TM; ++i) acc(i, j) = start;
   }
 
   float4 ra[A_LOADS];
@@ -159,9 +162,11 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
         b[g * 4 + 0] = vb.x; b[g * 4 + 1] = vb.y; b[g * 4 + 2] = vb.z; b[g * 4 + 3] = vb.w;
       }
 #pragma unroll
-      for (int i = 0; i < TM; ++i)
+      for (int i = 0; i < TM; ++i) {
+        const float2 a2 = make_float2(a[i], a[i]);
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < TN / 2; ++j) acc2[i][j] = __ffma2_rn(a2, make_float2(b[2 * j], b[2 * j + 1]), acc2[i][j]);
+      }
     }
     if (kb + 1 < num_kb) {
       stash(buf ^ 1);
@@ -176,8 +181,8 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
       const float add = (bias_last && n < N) ? __ldg(bias + n) : 0.f;
 #pragma unroll
       for (int i = 0; i < TM; ++i) {
-        float v = bias_last ? acc[i][j] + add : acc[i][j];
-        acc[i][j] = relu ? fmaxf(0.0f, v) : v;
+        float v = bias_last ? acc(i, j) + add : acc(i, j);
+        acc(i, j) = relu ? fmaxf(0.0f, v) : v;
       }
     }
   }
@@ -192,11 +197,11 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
       float* dst = C + int64_t(m) * ldc + n;
       if (vec_out && n + 4 <= N) {
         *reinterpret_cast<float4*>(dst) =
-            make_float4(acc[i][g * 4], acc[i][g * 4 + 1], acc[i][g * 4 + 2], acc[i][g * 4 + 3]);
+            make_float4(acc(i, g * 4), acc(i, g * 4 + 1), acc(i, g * 4 + 2), acc(i, g * 4 + 3));
       } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (n + j < N) dst[j] = acc[i][g * 4 + j];
+          if (n + j < N) dst[j] = acc(i, g * 4 + j);
       }
     }
   }
@@ -235,7 +240,7 @@ __device__ __forceinline__ float4 ks_ld_remote(const float* local_smem_ptr, uint
 }
 
 template <bool B_NK, bool VEC>
-__global__ void __launch_bounds__(kKsThreads, 7)
+__global__ void __launch_bounds__(kKsThreads, 6)
 sgemm_ffma_ksplit_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M,
                          int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int k_per_cta, int ks) {
   constexpr int T = kKsTile, LD = T + kPad;
@@ -251,11 +256,12 @@ sgemm_ffma_ksplit_kernel(const float* __restrict__ A, const float* __restrict__ 
   const int k_begin = int(rank) * k_per_cta;
   const int k_end = min(K, k_begin + k_per_cta);
 
-  float acc[8][8];
+  float2 acc2[8][4];  // pairs along n for the packed fp32 FMA
+  auto acc = [&](int i, int j) -> float& { return (j & 1) ? acc2[i][j >> 1].y : acc2[i][j >> 1].x; };
 #pragma unroll
   for (int i = 0; i < 8; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < 4; ++j) acc2[i][j] = make_float2(0.f, 0.f);
 
   float4 ra[4], rb[4];
   auto fetch = [&](int k0) {
@@ -303,9 +309,11 @@ sgemm_ffma_ksplit_kernel(const float* __restrict__ A, const float* __restrict__ 
         b[g * 4 + 0] = vb.x; b[g * 4 + 1] = vb.y; b[g * 4 + 2] = vb.z; b[g * 4 + 3] = vb.w;
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+      for (int i = 0; i < 8; ++i) {
+        const float2 a2 = make_float2(a[i], a[i]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) acc2[i][j] = __ffma2_rn(a2, make_float2(b[2 * j], b[2 * j + 1]), acc2[i][j]);
+      }
     }
     if (kb + 1 < num_kb) {
       stash(buf ^ 1);
@@ -321,7 +329,7 @@ sgemm_ffma_ksplit_kernel(const float* __restrict__ A, const float* __restrict__ 
     for (int i = 0; i < 8; ++i)
 #pragma unroll
       for (int g = 0; g < 2; ++g)
-        part[(i * 2 + g) * kKsThreads + tid] = make_float4(acc[i][g * 4], acc[i][g * 4 + 1], acc[i][g * 4 + 2], acc[i][g * 4 + 3]);
+        part[(i * 2 + g) * kKsThreads + tid] = make_float4(acc(i, g * 4), acc(i, g * 4 + 1), acc(i, g * 4 + 2), acc(i, g * 4 + 3));
   }
   ks_cluster_sync();
   if (rank == 0) {
@@ -331,7 +339,7 @@ sgemm_ffma_ksplit_kernel(const float* __restrict__ A, const float* __restrict__ 
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
           const float4 v = ks_ld_remote(reinterpret_cast<const float*>(&part[(i * 2 + g) * kKsThreads + tid]), uint32_t(r));
-          acc[i][g * 4 + 0] += v.x; acc[i][g * 4 + 1] += v.y; acc[i][g * 4 + 2] += v.z; acc[i][g * 4 + 3] += v.w;
+          acc(i, g * 4 + 0) += v.x; acc(i, g * 4 + 1) += v.y; acc(i, g * 4 + 2) += v.z; acc(i, g * 4 + 3) += v.w;
         }
     }
   }
@@ -348,11 +356,11 @@ sgemm_ffma_ksplit_kernel(const float* __restrict__ A, const float* __restrict__ 
       const int n = n0 + g * 32 + tx * 4;
       float* dst = C + int64_t(m) * ldc + n;
       if (vec_out && n + 4 <= N) {
-        *reinterpret_cast<float4*>(dst) = make_float4(acc[i][g * 4], acc[i][g * 4 + 1], acc[i][g * 4 + 2], acc[i][g * 4 + 3]);
+        *reinterpret_cast<float4*>(dst) = make_float4(acc(i, g * 4), acc(i, g * 4 + 1), acc(i, g * 4 + 2), acc(i, g * 4 + 3));
       } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (n + j < N) dst[j] = acc[i][g * 4 + j];
+          if (n + j < N) dst[j] = acc(i, g * 4 + j);
       }
     }
   }
@@ -409,7 +417,7 @@ int launch_shape(bool vec, const float* A, const float* B, float* C, int M, int 
     int ks = 0;
     if (g_ffma_ksplit > 0) ks = g_ffma_ksplit;
     else if (tiles64 <= 2 * 148 && K >= 512) ks = 4;   // e.g. 1024^3: 256 tiles x 4 = 1024 CTAs of 64 threads
-    else if (tiles64 <= 4 * 148 && K >= 512) ks = 2;
+    else if (tiles64 <= 8 * 148 && K >= 512) ks = 2;   // 2048^3: 344 us against 395 us for whole-K 128 x 128 tiles
     if (ks > 1 && K >= ks * BKF) return launch_ksplit<B_NK>(vec, ks, A, B, C, M, N, K, lda, ldb, ldc, stream);
   }
   // Largest tile whose grid still covers the machine (two CTAs fit on an SM): 128x128 once there
