@@ -91,7 +91,26 @@ sgemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
   float4 ra[A_LOADS];
   float4 rb[B_NK ? BT_LOADS : B_LOADS];
 
+  // A tile inside the matrices with K in whole slices loads through pointers worked out once, unchecked.
+  const bool interior = VEC && m0 + TBM <= M && n0 + TBN <= N && K % BKF == 0;
+  const float* pa0 = A + int64_t(m0 + (tid >> 2)) * lda + (tid & 3) * 4;  // load l: 64 rows below load l - 1
+  const float* pb0 = B_NK ? B + int64_t(n0 + (tid >> 2)) * ldb + (tid & 3) * 4
+                          : B + int64_t(tid / (TBN / 4)) * ldb + n0 + (tid % (TBN / 4)) * 4;
+  const int64_t pa_step = 64 * lda, pb_step = (B_NK ? 64 : kSgemmThreads / (TBN / 4)) * ldb;
   auto fetch = [&](int k0) {
+    if (interior) {
+#pragma unroll
+      for (int l = 0; l < A_LOADS; ++l) ra[l] = __ldg(reinterpret_cast<const float4*>(pa0 + l * pa_step + k0));
+      if constexpr (B_NK) {
+#pragma unroll
+        for (int l = 0; l < BT_LOADS; ++l) rb[l] = __ldg(reinterpret_cast<const float4*>(pb0 + l * pb_step + k0));
+      } else {
+#pragma unroll
+        for (int l = 0; l < B_LOADS; ++l)
+          rb[l] = __ldg(reinterpret_cast<const float4*>(pb0 + l * pb_step + int64_t(k0) * ldb));
+      }
+      return;
+    }
 #pragma unroll
     for (int l = 0; l < A_LOADS; ++l) {
       int idx = tid + l * kSgemmThreads;  // row = idx / 4, k-quad = idx % 4
