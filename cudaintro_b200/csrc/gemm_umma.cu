@@ -1325,7 +1325,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int quarter = warp & 3;
     const int r_in_tile = quarter * 32 + lane;
     const int row = m0 + r_in_tile;
-    if (mbar_wait_bounded(acc_full, 0u, abort_flag, p.wait_budget_ns)) {
+    if (mbar_wait_bounded_idle(acc_full, 0u, abort_flag, p.wait_budget_ns)) {
       tc_fence_after_sync();
       const uint32_t taddr = acc_base + (uint32_t(quarter * 32) << 16);
       const int big_ranges = min(T::NACC - 1, num_kb);

@@ -77,6 +77,27 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return true;
 }
 
+// The same for a warp that waits for something far away (an epilogue waiting for a whole main loop):
+// it sleeps between polls, so that it does not take issue slots from the warps that share its
+// scheduler while they work.
+__device__ __forceinline__ bool mbar_wait_bounded_idle(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                       uint64_t budget_ns = kWaitBudgetNs) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    __nanosleep(400);
+    if ((++spins & 0x3fu) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > budget_ns) {
+        *abort_flag = 1u;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------------------- TMA
 
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
