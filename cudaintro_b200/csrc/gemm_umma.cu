@@ -1080,7 +1080,7 @@ int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int
   // not by the tensor pipe: they take the kernel that splits the operands on chip (one hand-shake
   // per k-block instead of three, no scratch, one launch).  Large ones keep the split planes in
   // global memory and run on CTA pairs (measured on chip / split planes: 1024^3 29.7 / 48.4 us,
-  // 2048^3 127 / 145 us, 4096^3 901 / 743 us), except for very long sums: the pair kernel adds a
+  // 2048^3 113 / 147 us, 4096^3 797 / 725 us), except for very long sums: the pair kernel adds a
   // whole K into one accumulator, whose truncation error grows with K (9.6e-6 at K = 4096), while
   // the on-chip kernel sums K in ranges (4.9e-6 there).
   if (g_x3_path != 1 && x3_on_chip_applies(A, B, lda, ldb) &&
@@ -1112,8 +1112,8 @@ int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int
 // ------------------------------------------------------------------------------ 3xTF32, operands split on chip
 //
 // The same three-product fp32 GEMM without split planes in global memory.  TMA brings the fp32
-// tiles of A and B into a ring of "raw" stages.  Four converter warps split them: every thread owns
-// one row of the A tile, reads its 32 floats from the stage and writes the tf32 high parts (top 19
+// tiles of A and B into a ring of "raw" stages.  Eight converter warps split them: every thread owns
+// half a row of the A tile, reads its 16 floats from the stage and writes the tf32 high parts (top 19
 // bits) and the remainders, rounded to tf32, into tensor memory, where the MMA takes its A operand
 // from; B is cut to its high part in place and its remainder goes to one of two small shared-memory
 // buffers.  The MMA lane then issues lo*hi, hi*lo and hi*hi for the k-block.  Against the
@@ -1125,11 +1125,13 @@ int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int
 // an fp32 accumulator by truncation, so the error of one long chain grows in proportion to K;
 // short chains added with correctly rounded fp32 additions in the epilogue keep it small.
 // One tile of 128 x BN per CTA, no persistence; C is written from registers.
-//   warp 0 producer, warp 1 MMA + tensor memory, warps 2-5 epilogue, warps 6-9 converters.
+//   warp 0 producer, warp 1 MMA + tensor memory, warps 2-5 epilogue, warps 6-13 converters (two warps per
+//   32-row quarter of the A tile, each taking half of the k-block's columns).
 namespace b200 {
 namespace {
 
-constexpr int kX3Threads = 320;
+constexpr int kX3ConvThreads = 256;               // eight converter warps: two per quarter of tensor memory
+constexpr int kX3Threads = 192 + kX3ConvThreads;
 
 template <int BN>
 struct X3Tile {
@@ -1140,10 +1142,11 @@ struct X3Tile {
   static constexpr int SPAN = 32;                      // floats of N in one 128-byte span of an N-contiguous B
   static constexpr int NSPANS = BN / SPAN;
   static constexpr int SPAN_BYTES = BK * 128;
-  static constexpr int LO_BUFS = 2;                    // low parts of B (shared memory) and both parts of A (tensor memory)
+  static constexpr int LO_BUFS = 2;                    // low parts of B (shared memory) and both parts of A (tensor memory);
+                                                       // three changed nothing (1024^3: 29.5 against 29.7 us)
   static constexpr int STAGES_FIT = (kSmemBudget - 2048 - LO_BUFS * B_BYTES) / RAW_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
-  // Tensor memory, 512 columns: [0, 128) two A buffers of 32 high + 32 low columns; then NACC accumulators.
+  // Tensor memory, 512 columns: LO_BUFS A buffers of 32 high + 32 low columns each; then NACC accumulators.
   static constexpr int A_COLS = LO_BUFS * 2 * BK;
   static constexpr int NACC = (512 - A_COLS) / BN;
   static constexpr int TMEM_COLS = 512;
@@ -1181,7 +1184,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       mbar_init(&empty_bar[s], 1);
     }
     for (int j = 0; j < T::LO_BUFS; ++j) {
-      mbar_init(&lo_full[j], 128);  // every converter thread arrives
+      mbar_init(&lo_full[j], kX3ConvThreads);  // every converter thread arrives
       mbar_init(&lo_empty[j], 1);
     }
     mbar_init(acc_full, 1);
@@ -1269,9 +1272,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ converters
-    const int ct = int(threadIdx.x) - 6 * 32;  // 0..127
+    const int ct = int(threadIdx.x) - 6 * 32;  // 0..255
     const int quarter = warp & 3;              // the tensor-memory lanes this warp may touch
-    const int r = quarter * 32 + lane;         // row of the A tile this thread splits
+    const int half = (warp - 6) >> 2;          // which 16 of the k-block's 32 columns this warp splits
+    const int r = quarter * 32 + lane;         // row of the A tile this thread works on
     constexpr int B_CHUNKS = T::B_BYTES / 16;
     int stage = 0, j = 0;
     uint32_t phase = 0, lo_phase = 0;
@@ -1281,12 +1285,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       ok = __all_sync(0xffffffffu, ok) != 0;  // the warp stays together for the aligned tensor-memory stores
       if (!ok) break;
       tc_fence_after_sync();
-      // A: this thread's row, 8 swizzled 16-byte chunks -> 32 high and 32 low words in tensor memory
+      // A: half of this thread's row, 4 swizzled 16-byte chunks -> 16 high and 16 low words in tensor memory
       const uint8_t* arow = smem + stage * T::RAW_BYTES + r * 128;
-      uint32_t hi[32], lo[32];
+      uint32_t hi[16], lo[16];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 x = *reinterpret_cast<const uint4*>(arow + ((c ^ (r & 7)) << 4));
+      for (int c = 0; c < 4; ++c) {
+        const uint4 x = *reinterpret_cast<const uint4*>(arow + (((half * 4 + c) ^ (r & 7)) << 4));
         const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -1295,14 +1299,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           lo[4 * c + e] = __float_as_uint(round_to_tf32(__uint_as_float(xs[e]) - __uint_as_float(h)));
         }
       }
-      const uint32_t a_t = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(j * 2 * T::BK);
-      tmem_st_32x32(a_t, hi);
-      tmem_st_32x32(a_t + uint32_t(T::BK), lo);
+      const uint32_t a_t = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(j * 2 * T::BK + half * 16);
+      tmem_st_32x16(a_t, hi);
+      tmem_st_32x16(a_t + uint32_t(T::BK), lo);
       // B: element-wise on the stage's bytes, whatever their layout: high parts in place, low parts aside
       uint4* braw = reinterpret_cast<uint4*>(smem + stage * T::RAW_BYTES + T::A_BYTES);
       uint4* blo = reinterpret_cast<uint4*>(lo_base + j * T::B_BYTES);
 #pragma unroll 4
-      for (int c = ct; c < B_CHUNKS; c += 128) {
+      for (int c = ct; c < B_CHUNKS; c += kX3ConvThreads) {
         const uint4 x = braw[c];
         uint4 h, l;
         h.x = x.x & 0xffffe000u; h.y = x.y & 0xffffe000u; h.z = x.z & 0xffffe000u; h.w = x.w & 0xffffe000u;
