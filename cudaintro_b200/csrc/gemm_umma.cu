@@ -771,7 +771,8 @@ int launch_bn(int bn, int cg, bool b_nk, const void* A, const void* B, GemmArgs 
   if (args.group_m < 1) args.group_m = 1;
   if (cg == 2) {
     if (bn == 256) return launch_major<KIND, 256, EPI, 2>(b_nk, A, B, args, lda, ldb, stream);
-    return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs are built for 256-wide tiles only");
+    if (bn == 128) return launch_major<KIND, 128, EPI, 2>(b_nk, A, B, args, lda, ldb, stream);
+    return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs are built for 256- and 128-wide tiles only");
   }
   switch (bn) {
     case 256: return launch_major<KIND, 256, EPI, 1>(b_nk, A, B, args, lda, ldb, stream);
@@ -803,7 +804,7 @@ int set_tile_policy(int cg, int bn, int group_rows) {
   }
   if ((cg != 0 && cg != 1 && cg != 2) || (bn != 0 && bn != 64 && bn != 128 && bn != 256))
     return fail(B200_ERR_BAD_ARGUMENT, "tile policy: cta group must be 0, 1 or 2 and width 0, 64, 128 or 256");
-  if (cg == 2 && bn != 0 && bn != 256) return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs need 256-wide tiles");
+  if (cg == 2 && bn == 64) return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs need 256- or 128-wide tiles");
   g_force_cg = cg;
   g_force_bn = bn;
   g_group_rows = group_rows;
@@ -942,7 +943,7 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
     const int64_t pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
     cg = (bn == 0 || bn == 256) && M > BM && pair_tiles >= sms / 2 ? 2 : 1;  // a pair needs more than one CTA's rows
   }
-  if (cg == 2) bn = 256;
+  if (cg == 2 && bn == 0) bn = 256;
   if (bn == 0) {
     // Tile width with the smallest estimated time: waves of tiles over the SMs, each costing its
     // width plus a fixed part (pipeline fill, A traffic).  A narrow tile that spills into a second,
