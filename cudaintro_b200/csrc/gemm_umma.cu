@@ -43,28 +43,62 @@ namespace b200 {
 
 __device__ uint32_t g_umma_status = 0;  // bit 0: a bounded wait ran out somewhere
 
+// Wait accounting, compiled in only with -DB200_SKINNY_STAMPS (the measurement build; the shipped
+// library has none of it).  Every CTA adds up SM cycles into waits[cta][8]: 0 = MMA lane waiting for
+// full stages, 1 = MMA lane waiting for a free accumulator, 2 = MMA lane's whole loop, 3 = producer
+// lane waiting for free stages, 4 = producer lane's whole loop, 5 = epilogue (warp 2) waiting for
+// accumulators, 6 = epilogue's whole loop, 7 = k-blocks whose stage was not yet full when asked for,
+// 8 = epilogue from "accumulator complete" to "accumulator handed back", 9 = the storing thread
+// waiting for the previous tile store to have read its buffer, 10 = the same thread at the barrier.
+// Eight-warp epilogue (warp 2): 9 = that wait, 11 = tensor-memory loads, 12 = convert and stage,
+// 13 = fence and store issue.
+#ifdef B200_SKINNY_STAMPS
+__device__ unsigned long long* g_umma_waits = nullptr;
+#define UW_DECL(name) long long name = 0
+#define UW_BEGIN(name) name -= clock64()
+#define UW_END(name) name += clock64()
+#define UW_PUT(slot, value)                                                                        \
+  do {                                                                                             \
+    if (g_umma_waits != nullptr) g_umma_waits[size_t(blockIdx.x) * 16 + (slot)] = (unsigned long long)(value); \
+  } while (0)
+#else
+#define UW_DECL(name) do { } while (0)
+#define UW_BEGIN(name) do { } while (0)
+#define UW_END(name) do { } while (0)
+#define UW_PUT(slot, value) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int BM = 128;          // rows of C per tile = TMEM lanes
 constexpr int kThreads = 192;    // producer warp, MMA warp, four epilogue warps
+constexpr int kThreadsRB2 = 320; // two row blocks per CTA: eight epilogue warps, each storing on its own
 constexpr int kSmemBudget = 227 * 1024;
 
 bool g_use_pdl = true;  // launch the GEMM kernel with programmatic stream serialisation
 
 // CG = 1: one CTA owns a 128 x BN tile.  CG = 2: a pair of CTAs (cluster of 2) owns a 256 x BN tile;
 // each CTA stages its own 128 rows of A and its own BN/2 columns of B, and the even-ranked CTA
-// issues tcgen05.mma.cta_group::2 for both.
-template <int KIND, int BN_, int CG_ = 1>
+// issues tcgen05.mma.cta_group::2 for both.  RB = 2 (pairs only): every CTA owns two 128-row blocks
+// of A, so the pair's tile is 512 x BN.  A k-block of B then feeds twice the arithmetic, which cuts
+// the bytes an SM pulls from L2 per flop by a quarter; the price is that the two accumulators
+// (2 x BN columns) fill tensor memory, so a tile's epilogue no longer overlaps the next tile's MMAs.
+template <int KIND, int BN_, int CG_ = 1, int RB_ = 1>
 struct Tile {
   static constexpr int ELEM = KIND == KIND_I8 ? 1 : (KIND == KIND_TF32 ? 4 : 2);
   static constexpr int BN = BN_;
   static constexpr int CG = CG_;
+  static constexpr int RB = RB_;
+  static constexpr int ACC_BUFS = RB_ == 2 ? 1 : 2;  // accumulator sets in tensor memory (two = epilogue overlaps the next tile)
+  static constexpr int EPI_WARPS = RB_ == 2 ? 8 : 4;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+  static constexpr int C_BOX_ROWS = RB_ == 2 ? 32 : BM;  // rows of one TMA store: a warp's own rows, or the tile's
   static constexpr int BN_CTA = BN / CG;     // B columns staged by one CTA
   static constexpr int BK = 128 / ELEM;      // elements of K per stage (one 128-byte swizzle row)
   static constexpr int UMMA_K = 32 / ELEM;   // elements of K per tcgen05.mma
   static constexpr int SPAN = 128 / ELEM;    // elements of N in one 128-byte span (MN-major B)
   static constexpr int NSPANS = BN_CTA / SPAN;
-  static constexpr int A_BYTES = BM * 128;
+  static constexpr int A_BYTES = RB * BM * 128;
   static constexpr int B_BYTES = BN_CTA * 128;
   static constexpr int SPAN_BYTES = BK * 128;  // one span of B: BK k-rows of 128 bytes
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -72,7 +106,8 @@ struct Tile {
   static constexpr int STAGING_BYTES = NSTG * BM * 128;  // two 128-row x 128-byte output tiles for the TMA stores
   static constexpr int STAGES_FIT = (kSmemBudget - 2048 - STAGING_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // BN is a power of two here
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // BN is a power of two here; RB * ACC_BUFS = 2 always
+  static_assert(RB == 1 || (RB == 2 && CG == 2 && BN == 256), "two row blocks per CTA: pairs with 256-wide tiles only");
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
@@ -147,6 +182,21 @@ __device__ __forceinline__ void pack_chunk(const GemmArgs& p, int n0, const uint
       }
     }
   } else {
+    if constexpr (EPI == EPI_F16 || EPI == EPI_BF16) {
+      if (p.bias == nullptr && !relu) {  // the plain product: one packed conversion per pair, nothing else
+#pragma unroll
+        for (int i = 0; i < W / 2; ++i) {
+          if constexpr (EPI == EPI_F16) {
+            __half2 h = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        return;
+      }
+    }
     // W8A8: the chunk's column scales, four per load where the chunk lies inside C and the scales
     // are 16-byte aligned (every thread of the warp reads the same addresses: one broadcast each).
     [[maybe_unused]] float cs[W];
@@ -220,12 +270,13 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int n0, 
   }
 }
 
-template <int KIND, int BN, bool B_NK, int EPI, int CG>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int KIND, int BN, bool B_NK, int EPI, int CG, int RB = 1>
+__global__ void __launch_bounds__(RB == 2 ? kThreadsRB2 : kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CMaps tmap_c, const GemmArgs p) {
-  using T = Tile<KIND, BN, CG>;
-  constexpr int TILE_M = BM * CG;
+  using T = Tile<KIND, BN, CG, RB>;
+  constexpr int TILE_M = BM * CG * RB;
+  constexpr int CTA_M = BM * RB;  // rows of the tile this CTA stages and stores
   constexpr int NSTG = T::NSTG;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes: align the stage ring to that.
@@ -262,7 +313,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4 * CG);  // one arrival per epilogue warp (of both CTAs of a pair)
+      mbar_init(&acc_empty[b], T::EPI_WARPS * CG);  // one arrival per epilogue warp (of both CTAs of a pair)
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -299,6 +350,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int it = 0;
       const uint64_t pol_a = (p.l2_hints & 1) ? l2_policy_evict_last() : l2_policy_evict_normal();
       const uint64_t pol_b = (p.l2_hints & 2) ? l2_policy_evict_first() : l2_policy_evict_normal();
+      UW_DECL(w_empty); UW_DECL(w_all);
+      UW_BEGIN(w_all);
       for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
         int mb, nb;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
@@ -306,7 +359,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // touched last, which are the ones still in L2 (a forward-only sweep over a slab larger
         // than the cache would evict each block just before it is needed again).
         const bool k_reversed = (it & 1) != 0;
-        const int m0 = mb * TILE_M + int(cta_rank) * BM;
+        const int m0 = mb * TILE_M + int(cta_rank) * CTA_M;
         const int n0 = nb * BN + int(cta_rank) * T::BN_CTA;
         // (pass, kin) = (kbt / num_kb, kbt % num_kb), counted rather than divided: this lane's loop paces
         // the CTA and an integer division per k-block is not free in it.
@@ -315,7 +368,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int kb = k_reversed ? num_kb - 1 - kin : kin;
           const int a_row0 = (X3 && pass != 0) ? p.M : 0;                       // plane 1 = high parts
           const int b_row0 = (X3 && pass != 1) ? (B_NK ? p.N : p.K) : 0;
-          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.wait_budget_ns)) { ok = false; break; }
+          UW_BEGIN(w_empty);
+          const bool stage_free = mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.wait_budget_ns);
+          UW_END(w_empty);
+          if (!stage_free) { ok = false; break; }
           if (kbt == p.lose_kb && it == 0 && blockIdx.x == 0) {
             // Test of the give-up path: this stage is never filled and never announced, as if its
             // arrival had been lost.  The MMA lane's wait for it runs out and the CTA drains.
@@ -354,6 +410,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (++kin == num_kb) { kin = 0; ++pass; }
         }
       }
+      UW_END(w_all);
+      UW_PUT(3, w_empty);
+      UW_PUT(4, w_all);
       if constexpr (CG == 2) {
         // Stay until every stage this CTA filled has been released: the releases are arrivals sent
         // by the leader's MMA commits into this CTA's shared memory, which must still exist.
@@ -366,7 +425,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && cta_rank == 0) {
-      constexpr uint32_t idesc = make_instr_desc(KIND, TILE_M, BN, 0, B_NK ? 0 : 1);
+      constexpr uint32_t idesc = make_instr_desc(KIND, BM * CG, BN, 0, B_NK ? 0 : 1);
       // Operand descriptors of stage 0; a later stage's differ in the address field only, which is in
       // units of 16 bytes and cannot carry out of its 14 bits for addresses inside shared memory.  This
       // lane's loop feeds the tensor pipe, so the descriptors are stepped, not rebuilt, per k-block.
@@ -383,14 +442,25 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      UW_DECL(w_full); UW_DECL(w_acc); UW_DECL(w_all); UW_DECL(late);
+      UW_BEGIN(w_all);
       for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
-        const int ab = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait_bounded(&acc_empty[ab], acc_phase ^ 1u, abort_flag, p.wait_budget_ns)) break;
+        const int ab = it % T::ACC_BUFS;
+        const uint32_t acc_phase = (it / T::ACC_BUFS) & 1;
+        UW_BEGIN(w_acc);
+        const bool acc_free = mbar_wait_bounded(&acc_empty[ab], acc_phase ^ 1u, abort_flag, p.wait_budget_ns);
+        UW_END(w_acc);
+        if (!acc_free) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);
+        const uint32_t d_tmem = tmem_base + uint32_t(ab * BN);  // with two row blocks: block 1 at + BN
         for (int kb = 0; kb < total_kb; ++kb) {
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.wait_budget_ns)) { ok = false; break; }
+#ifdef B200_SKINNY_STAMPS
+          if (!mbar_try_wait(&full_bar[stage], phase)) ++late;
+#endif
+          UW_BEGIN(w_full);
+          const bool stage_full = mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.wait_budget_ns);
+          UW_END(w_full);
+          if (!stage_full) { ok = false; break; }
           tc_fence_after_sync();
 #pragma unroll
           for (int j = 0; j < T::BK / T::UMMA_K; ++j) {
@@ -398,10 +468,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // B advances UMMA_K whole k-rows of 128 bytes.
             const uint64_t a_adv = uint64_t((j * 32) >> 4);
             const uint64_t b_adv = B_NK ? uint64_t((j * 32) >> 4) : uint64_t((j * T::UMMA_K * 128) >> 4);
-            if constexpr (CG == 2)
-              umma_pair<KIND>(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, (kb | j) != 0 ? 1u : 0u);
-            else
+            if constexpr (CG == 2) {
+#pragma unroll
+              for (int rb = 0; rb < RB; ++rb)  // both row blocks take the same slice of B
+                umma_pair<KIND>(d_tmem + uint32_t(rb * BN), a_desc + uint64_t((rb * BM * 128) >> 4) + a_adv,
+                                b_desc + b_adv, idesc, (kb | j) != 0 ? 1u : 0u);
+            } else {
               umma<KIND>(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, (kb | j) != 0 ? 1u : 0u);
+            }
           }
           // the stage is free (in both CTAs of a pair) once these MMAs have read it
           if constexpr (CG == 2) umma_commit_pair(&empty_bar[stage], 3); else umma_commit(&empty_bar[stage]);
@@ -413,6 +487,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if constexpr (CG == 2) umma_commit_pair(&acc_full[ab], 3); else umma_commit(&acc_full[ab]);
         }
       }
+      UW_END(w_all);
+      UW_PUT(0, w_full);
+      UW_PUT(1, w_acc);
+      UW_PUT(2, w_all);
+      UW_PUT(7, late);
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
@@ -427,26 +506,207 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t boxes = 0;
     int it = 0;
     const uint64_t pol_c = (p.l2_hints & 4) ? l2_policy_evict_first() : l2_policy_evict_normal();
+    UW_DECL(w_accfull); UW_DECL(w_all); UW_DECL(w_drain); UW_DECL(w_rd); UW_DECL(w_bar);
+    UW_BEGIN(w_all);
+    if constexpr (RB == 2) {
+      // Eight warps, two per 32-lane quarter of tensor memory; warps 2-5 drain row block 0, warps 6-9
+      // row block 1.  Nothing here overlaps the next tile's MMAs (the accumulators fill tensor memory), so
+      // the drain is what the tensor pipe waits for: once a tile's accumulators are there, every warp works
+      // alone, without a barrier shared with the others.  It stages its own 32 rows x 128 bytes, stores them with a TMA request of its
+      // own, and hands the accumulators back as soon as its last values are in registers.
+      const int group = (warp - 2) >> 2;  // = row block
+      UW_DECL(w_ld); UW_DECL(w_cv); UW_DECL(w_st);
+      uint8_t* buf = staging + (warp - 2) * (32 * 128);
+      uint32_t stores = 0;
+      for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
+        int mb, nb;
+        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+        const uint32_t acc_phase = it & 1;
+        volatile uint32_t* epi_go = epi_go_pair + (it & 1);
+        // One warp polls the barrier; the other seven sleep at a hardware barrier meanwhile (a main
+        // loop lasts tens of microseconds, and 256 polling threads are power the tensor pipe could use).
+        UW_BEGIN(w_accfull);
+        if (warp == 2) {
+          const bool ok = mbar_wait_bounded(&acc_full[0], acc_phase, abort_flag, p.wait_budget_ns);
+          if (lane == 0) *epi_go = ok ? 1u : 0u;
+        }
+        named_barrier_sync(2, 32 * T::EPI_WARPS);
+        UW_END(w_accfull);
+        if (*epi_go == 0u) break;
+        tc_fence_after_sync();
+        UW_BEGIN(w_drain);
+        const int row0 = mb * TILE_M + int(cta_rank) * CTA_M + group * BM + quarter * 32;  // this warp's first row of C
+        const int row = row0 + lane;
+        float rs = 0.f;
+        if constexpr (EPI == EPI_W8A8_BF16) rs = row < p.M ? __ldg(p.row_scale + row) : 0.f;
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(group * BN);
+        const int cols_left = p.N - nb * BN;
+        const int nboxes = min(BN / BOX_COLS, (cols_left + BOX_COLS - 1) / BOX_COLS);
+        if constexpr (OUT_BYTES == 2) {
+          // 2-byte outputs: the warp's whole share of the tile (32 rows x 256 columns) fits in registers
+          // once converted (128 words a thread).  Convert everything first, hand the accumulators
+          // back, and only then stage and store: the MMA lane waits for the conversions alone.
+          if (p.store_mode == STORE_TMA) {
+            constexpr int NB = BN / BOX_COLS;  // 4 boxes of 64 columns
+            uint32_t packed[NB][CHUNKS_PER_BOX][16];
+            UW_BEGIN(w_ld);
+#pragma unroll
+            for (int bx = 0; bx < NB; ++bx) {
+              if (bx < nboxes) {
+#pragma unroll
+                for (int q = 0; q < 2 * CHUNKS_PER_BOX; ++q) {  // 16 columns at a time: few live registers beside `packed`
+                  uint32_t v[16], w[16];
+                  tmem_ld_32x16(taddr + uint32_t(bx * BOX_COLS + q * 16), v);
+                  tmem_ld_wait();
+                  pack_chunk<EPI, 16>(p, nb * BN + bx * BOX_COLS + q * 16, v, rs, w);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) packed[bx][q >> 1][(q & 1) * 8 + i] = w[i];
+                }
+              }
+            }
+            UW_END(w_ld);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[0]), 0));
+            UW_END(w_drain);
+#pragma unroll
+            for (int bx = 0; bx < NB; ++bx) {
+              if (bx < nboxes) {
+                const int n0 = nb * BN + bx * BOX_COLS;
+                UW_BEGIN(w_rd);
+                if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
+                __syncwarp();
+                UW_END(w_rd);
+                UW_BEGIN(w_cv);
+#pragma unroll
+                for (int h = 0; h < CHUNKS_PER_BOX; ++h)
+#pragma unroll
+                  for (int i = 0; i < UNITS; ++i) {
+                    const int unit = h * UNITS + i;
+                    *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) = make_uint4(
+                        packed[bx][h][4 * i], packed[bx][h][4 * i + 1], packed[bx][h][4 * i + 2], packed[bx][h][4 * i + 3]);
+                  }
+                UW_END(w_cv);
+                UW_BEGIN(w_st);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && row0 < p.M) {
+                  if (p.n_dest > 1) {  // peers first, from a start that rotates; the local copy last
+                    const int peers = p.n_dest - 1;
+                    int g = 1 + int((uint32_t(first_tile) + stores) % uint32_t(peers));
+                    for (int i = 0; i < peers; ++i) {
+                      tma_store_2d_hint(&tmap_c.m[g], buf, n0, row0, pol_c);
+                      if (++g == p.n_dest) g = 1;
+                    }
+                  }
+                  tma_store_2d_hint(&tmap_c.m[0], buf, n0, row0, pol_c);
+                  tma_store_commit();
+                }
+                UW_END(w_st);
+                ++stores;
+              }
+            }
+            continue;
+          }
+        }
+#pragma unroll 1
+        for (int bx = 0; bx < nboxes; ++bx) {
+          const int n0 = nb * BN + bx * BOX_COLS;
+          uint32_t v[CHUNKS_PER_BOX][32];
+          UW_BEGIN(w_ld);
+#pragma unroll
+          for (int h = 0; h < CHUNKS_PER_BOX; ++h) tmem_ld_32x32(taddr + uint32_t(bx * BOX_COLS + h * 32), v[h]);
+          tmem_ld_wait();
+          UW_END(w_ld);
+          if (bx + 1 == nboxes) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[0]), 0));
+            UW_END(w_drain);
+          }
+          if (p.store_mode == STORE_TMA) {
+            UW_BEGIN(w_rd);
+            if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
+            __syncwarp();
+            UW_END(w_rd);
+            UW_BEGIN(w_cv);
+#pragma unroll
+            for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
+              uint32_t w[32];
+              pack_chunk<EPI>(p, n0 + h * 32, v[h], rs, w);
+#pragma unroll
+              for (int i = 0; i < UNITS; ++i) {
+                const int unit = h * UNITS + i;
+                *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) =
+                    make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+              }
+            }
+            UW_END(w_cv);
+            UW_BEGIN(w_st);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {
+              if (p.n_dest > 1) {  // peers first, from a start that rotates; the local copy last
+                const int peers = p.n_dest - 1;
+                int g = 1 + int((uint32_t(first_tile) + stores) % uint32_t(peers));
+                for (int i = 0; i < peers; ++i) {
+                  tma_store_2d_hint(&tmap_c.m[g], buf, n0, row0, pol_c);
+                  if (++g == p.n_dest) g = 1;
+                }
+              }
+              tma_store_2d_hint(&tmap_c.m[0], buf, n0, row0, pol_c);
+              tma_store_commit();
+            }
+            UW_END(w_st);
+            ++stores;
+          } else {
+#pragma unroll
+            for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
+              uint32_t w[32];
+              pack_chunk<EPI>(p, n0 + h * 32, v[h], rs, w);
+              if (row < p.M && n0 + h * 32 < p.N) store_chunk<EPI>(p, row, n0 + h * 32, w);
+            }
+          }
+        }
+      }
+      UW_END(w_all);
+      if (store_thread) {
+        UW_PUT(5, w_accfull);
+        UW_PUT(6, w_all);
+        UW_PUT(8, w_drain);
+        UW_PUT(9, w_rd);
+        UW_PUT(11, w_ld);
+        UW_PUT(12, w_cv);
+        UW_PUT(13, w_st);
+      }
+      if (lane == 0 && p.store_mode == STORE_TMA) tma_store_wait_all<0>();
+    } else {
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mb, nb;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
-      const int ab = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
-      volatile uint32_t* epi_go = epi_go_pair + ab;
+      const int ab = it % T::ACC_BUFS;
+      const uint32_t acc_phase = (it / T::ACC_BUFS) & 1;
+      volatile uint32_t* epi_go = epi_go_pair + (it & 1);
       // One warp polls the barrier; all four then agree on the outcome, so that they always meet at
       // the same hardware barriers below even when the wait had to be given up.
       if (warp == 2) {
+        UW_BEGIN(w_accfull);
         const bool ok = mbar_wait_bounded(&acc_full[ab], acc_phase, abort_flag, p.wait_budget_ns);
+        UW_END(w_accfull);
         if (lane == 0) *epi_go = ok ? 1u : 0u;
       }
       named_barrier_sync(2, kEpiThreads);
       if (*epi_go == 0u) break;
       tc_fence_after_sync();
-      const int tile_row0 = mb * TILE_M + int(cta_rank) * BM;
+      UW_BEGIN(w_drain);
+      bool released = false;  // this warp has handed the accumulators back to the MMA lane
+#pragma unroll 1
+      for (int rb = 0; rb < RB; ++rb) {
+      const int tile_row0 = mb * TILE_M + int(cta_rank) * CTA_M + rb * BM;
       const int row = tile_row0 + r_in_tile;
       float rs = 0.f;
       if constexpr (EPI == EPI_W8A8_BF16) rs = row < p.M ? __ldg(p.row_scale + row) : 0.f;
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(ab * BN);
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(ab * BN + rb * BN);
       if (p.store_mode >= STORE_TMA) {
         // Stage 128 x 128-byte output tiles ("boxes") in shared memory, swizzled like the tensor map
         // expects, and let TMA write them: whole rows per request, clipped at the edges of C, one
@@ -474,6 +734,17 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int h = 0; h < CHUNKS_PER_BOX; ++h)
               tmem_ld_32x32(taddr + uint32_t((bx + 1) * BOX_COLS + h * 32), vn[h]);
+          } else if (rb + 1 == RB) {
+            // The tile's last values are in registers: the MMA lane may have the accumulators back
+            // while this box is converted and stored.
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[ab]), 0));
+              else mbar_arrive(&acc_empty[ab]);
+            }
+            released = true;
+            UW_END(w_drain);
           }
 #pragma unroll
           for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
@@ -508,8 +779,12 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             continue;
           }
           fence_proxy_async_smem();
+          UW_BEGIN(w_rd);
           if (store_thread) tma_store_wait_read<0>();  // the other buffer is free for the next box
+          UW_END(w_rd);
+          UW_BEGIN(w_bar);
           named_barrier_sync(1, kEpiThreads);
+          UW_END(w_bar);
           if (store_thread) {
             // Destination 0 (by convention the local copy) goes last; the others (peer GPUs) are
             // walked from a start that rotates with the CTA and the box count, so that every sender
@@ -540,14 +815,27 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (row < p.M) store_chunk<EPI>(p, row, n0, w);
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[ab]), 0));
-        else mbar_arrive(&acc_empty[ab]);
+      }  // row blocks
+      if (!released) {
+        UW_END(w_drain);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CG == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[ab]), 0));
+          else mbar_arrive(&acc_empty[ab]);
+        }
       }
     }
+    UW_END(w_all);
+    if (store_thread) {
+      UW_PUT(5, w_accfull);
+      UW_PUT(6, w_all);
+      UW_PUT(8, w_drain);
+      UW_PUT(9, w_rd);
+      UW_PUT(10, w_bar);
+    }
     if (store_thread && p.store_mode == STORE_TMA) tma_store_wait_all<0>();  // every output tile has left for global memory
+    }  // four-warp epilogue
   }
 
   // Every role gets here: either its loop ended or its wait was abandoned.
@@ -611,7 +899,7 @@ int make_map(CUtensorMap* map, int kind, const void* base, int64_t rows, int64_t
 }
 
 // Tensor map for storing 128-row x 128-byte tiles of a row-major [rows, cols] C.
-int make_c_map(CUtensorMap* map, int epi, void* base, int64_t rows, int64_t cols, int64_t ld) {
+int make_c_map(CUtensorMap* map, int epi, void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const int elem = (epi == EPI_I32 || epi == EPI_F32) ? 4 : 2;
@@ -621,13 +909,25 @@ int make_c_map(CUtensorMap* map, int epi, void* base, int64_t rows, int64_t cols
                                             : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
   cuuint64_t strides[1] = {cuuint64_t(ld) * cuuint64_t(elem)};
-  cuuint32_t box[2] = {cuuint32_t(128 / elem), cuuint32_t(BM)};
+  cuuint32_t box[2] = {cuuint32_t(128 / elem), cuuint32_t(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled (C) failed with CUresult %d", int(r));
   return B200_OK;
 }
+
+#ifdef B200_SKINNY_STAMPS
+}  // namespace
+}  // namespace b200
+// Measurement build only: where the GEMM kernel writes its wait accounting (16 words per CTA), or null.
+extern "C" int b200_debug_set_umma_waits(void* device_buffer) {
+  unsigned long long* p = static_cast<unsigned long long*>(device_buffer);
+  return cudaMemcpyToSymbol(b200::g_umma_waits, &p, sizeof(p)) == cudaSuccess ? 0 : 3;
+}
+namespace b200 {
+namespace {
+#endif
 
 int sm_count_of_current_device(int* out) {
   static int cached[64] = {0};
@@ -641,11 +941,11 @@ int sm_count_of_current_device(int* out) {
   return B200_OK;
 }
 
-template <int KIND, int BN, bool B_NK, int EPI, int CG>
+template <int KIND, int BN, bool B_NK, int EPI, int CG, int RB = 1>
 int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb,
                cudaStream_t stream) {
-  using T = Tile<KIND, BN, CG>;
-  auto kernel = gemm_umma_kernel<KIND, BN, B_NK, EPI, CG>;
+  using T = Tile<KIND, BN, CG, RB>;
+  auto kernel = gemm_umma_kernel<KIND, BN, B_NK, EPI, CG, RB>;
   // The shared-memory attribute is per device: set it whenever this thread meets a new device.
   static thread_local int last_dev = -1;
   int dev = 0;
@@ -659,7 +959,7 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
   }
   CUtensorMap ma, mb;
   const int64_t planes = (KIND == KIND_TF32 && !args.single_pass) ? 2 : 1;  // split fp32 operands: low plane, then high plane
-  int rc = make_map(&ma, KIND, A, planes * args.M, args.K, lda, T::BK, BM);
+  int rc = make_map(&ma, KIND, A, planes * args.M, args.K, lda, T::BK, BM * RB);
   if (rc) return rc;
   if (B_NK)
     rc = make_map(&mb, KIND, B, planes * args.N, args.K, ldb, T::BK, T::BN_CTA);
@@ -671,7 +971,7 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
   memset(&mc, 0, sizeof(mc));
   if (args.store_mode == STORE_TMA) {
     for (int g = 0; g < args.n_dest; ++g) {
-      rc = make_c_map(&mc.m[g], EPI, args.C[g], args.M, args.N, args.ldc);
+      rc = make_c_map(&mc.m[g], EPI, args.C[g], args.M, args.N, args.ldc, T::C_BOX_ROWS);
       if (rc) return rc;
     }
   }
@@ -684,7 +984,7 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
   // stream is still draining; they touch no global data before griddepcontrol.wait, which holds them
   // until that kernel has completed.
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(T::THREADS);
   cfg.dynamicSmemBytes = T::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -711,17 +1011,17 @@ int launch_one(const void* A, const void* B, const GemmArgs& args, int64_t lda, 
   return B200_OK;
 }
 
-template <int KIND, int BN, int EPI, int CG>
+template <int KIND, int BN, int EPI, int CG, int RB = 1>
 int launch_major(bool b_nk, const void* A, const void* B, const GemmArgs& args, int64_t lda, int64_t ldb,
                  cudaStream_t stream) {
   // An N-contiguous B is staged in whole 128-byte spans of N, so a CTA's share of the tile cannot be
   // narrower than one span.
   if constexpr (BN / CG < Tile<KIND, BN, CG>::SPAN) {
     if (!b_nk) return fail(B200_ERR_BAD_ARGUMENT, "tile width %d is narrower than a 128-byte span", BN / CG);
-    return launch_one<KIND, BN, true, EPI, CG>(A, B, args, lda, ldb, stream);
+    return launch_one<KIND, BN, true, EPI, CG, RB>(A, B, args, lda, ldb, stream);
   } else {
-    return b_nk ? launch_one<KIND, BN, true, EPI, CG>(A, B, args, lda, ldb, stream)
-                : launch_one<KIND, BN, false, EPI, CG>(A, B, args, lda, ldb, stream);
+    return b_nk ? launch_one<KIND, BN, true, EPI, CG, RB>(A, B, args, lda, ldb, stream)
+                : launch_one<KIND, BN, false, EPI, CG, RB>(A, B, args, lda, ldb, stream);
   }
 }
 
@@ -763,16 +1063,17 @@ int scratch_pool(cudaMemPool_t* out) {
 }
 
 template <int KIND, int EPI>
-int launch_bn(int bn, int cg, bool b_nk, const void* A, const void* B, GemmArgs args, int64_t lda, int64_t ldb,
+int launch_bn(int bn, int cg, int rb, bool b_nk, const void* A, const void* B, GemmArgs args, int64_t lda, int64_t ldb,
               cudaStream_t stream) {
+  const int tile_m = BM * cg * rb;
   args.tiles_n = int((args.N + bn - 1) / bn);
-  args.tiles_m = int((args.M + BM * cg - 1) / (BM * cg));
-  args.group_m = (g_group_rows ? g_group_rows : kDefaultGroupRows) / (BM * cg);
+  args.tiles_m = int((args.M + tile_m - 1) / tile_m);
+  args.group_m = (g_group_rows ? g_group_rows : kDefaultGroupRows) / tile_m;
   if (args.group_m < 1) args.group_m = 1;
   if (cg == 2) {
+    if (bn == 256 && rb == 2) return launch_major<KIND, 256, EPI, 2, 2>(b_nk, A, B, args, lda, ldb, stream);
     if (bn == 256) return launch_major<KIND, 256, EPI, 2>(b_nk, A, B, args, lda, ldb, stream);
-    if (bn == 128) return launch_major<KIND, 128, EPI, 2>(b_nk, A, B, args, lda, ldb, stream);
-    return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs are built for 256- and 128-wide tiles only");
+    return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs are built for 256-wide tiles only");
   }
   switch (bn) {
     case 256: return launch_major<KIND, 256, EPI, 1>(b_nk, A, B, args, lda, ldb, stream);
@@ -802,9 +1103,9 @@ int set_tile_policy(int cg, int bn, int group_rows) {
     g_group_rows = group_rows;
     return B200_OK;
   }
-  if ((cg != 0 && cg != 1 && cg != 2) || (bn != 0 && bn != 64 && bn != 128 && bn != 256))
-    return fail(B200_ERR_BAD_ARGUMENT, "tile policy: cta group must be 0, 1 or 2 and width 0, 64, 128 or 256");
-  if (cg == 2 && bn == 64) return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs need 256- or 128-wide tiles");
+  if ((cg != 0 && cg != 1 && cg != 2 && cg != 4) || (bn != 0 && bn != 64 && bn != 128 && bn != 256))
+    return fail(B200_ERR_BAD_ARGUMENT, "tile policy: cta group must be 0, 1, 2 or 4 and width 0, 64, 128 or 256");
+  if (cg >= 2 && bn != 0 && bn != 256) return fail(B200_ERR_BAD_ARGUMENT, "CTA pairs need 256-wide tiles");
   g_force_cg = cg;
   g_force_bn = bn;
   g_group_rows = group_rows;
@@ -843,7 +1144,7 @@ int read_and_clear_umma_status(cudaStream_t stream, uint32_t* out) {
 }
 
 namespace {
-int launch_kind(int kind, int epi, int bn, int cg, bool b_is_nk, const void* A, const void* B, const GemmArgs& args,
+int launch_kind(int kind, int epi, int bn, int cg, int rb, bool b_is_nk, const void* A, const void* B, const GemmArgs& args,
                 int64_t lda, int64_t ldb, cudaStream_t stream);
 }
 
@@ -938,12 +1239,29 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
     return fail(B200_ERR_UNSUPPORTED, "the skinny kernel takes fp16, bf16 and int8 products with one destination");
   int bn = force_bn ? force_bn : (skinny_forced ? 0 : g_force_bn);
   int cg = skinny_forced ? 1 : g_force_cg;
+  int rb = 1;
+  if (cg == 4) { cg = 2; rb = 2; }  // tile policy 4: CTA pairs with two row blocks per CTA (512 x 256 tiles)
+  if (g_multicast_call) rb = 1;     // the multicast epilogue is the four-warp one
   if (cg == 0) {
     // CTA pairs (256 x 256 tiles) once they give every pair of SMs a tile; single CTAs below that.
     const int64_t pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
     cg = (bn == 0 || bn == 256) && M > BM && pair_tiles >= sms / 2 ? 2 : 1;  // a pair needs more than one CTA's rows
+    // Two row blocks per CTA (512 x 256 tiles): a quarter fewer bytes from L2 per flop against an
+    // epilogue that the next tile's MMAs no longer hide.  Measured back to back from a cool start,
+    // 256-row / 512-row tiles: tf32 8192^3 1550 / 1306 us, 4096^3 213 / 180 us; bf16 8192^3 718 / 676 us,
+    // 4096^3 99.8 / 95.5 us; int8 8192^3 339 / 339 us, 4096^3 52.6 / 55.6 us.  In long runs under the
+    // power cap the 16-bit gain shrinks to nothing below K = 8192 (4096^3: 126 / 134 us, 6144^3: 307 /
+    // 309 us), so: tf32 (twice the bytes per flop) takes them whenever they cost at most one extra wave
+    // in eight, 16-bit kinds for K >= 8192 where they cost no extra wave, int8 never.
+    if (cg == 2 && !g_multicast_call && kind != KIND_I8) {
+      const int64_t pairs = sms / 2;
+      const int64_t tiles_n = (N + 255) / 256;
+      const int64_t waves256 = (pair_tiles + pairs - 1) / pairs;
+      const int64_t waves512 = 2 * ((((M + 4 * BM - 1) / (4 * BM)) * tiles_n + pairs - 1) / pairs);
+      if (kind == KIND_TF32 ? waves512 * 7 <= waves256 * 8 : (K >= 8192 && waves512 <= waves256)) rb = 2;
+    }
   }
-  if (cg == 2 && bn == 0) bn = 256;
+  if (cg == 2) bn = 256;
   if (bn == 0) {
     // Tile width with the smallest estimated time: waves of tiles over the SMs, each costing its
     // width plus a fixed part (pipeline fill, A traffic).  A narrow tile that spills into a second,
@@ -972,28 +1290,28 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
     if (rc || used) return rc;
   }
 
-  return launch_kind(kind, epi, bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
+  return launch_kind(kind, epi, bn, cg, rb, b_is_nk, A, B, args, lda, ldb, stream);
 }
 
 namespace {
-int launch_kind(int kind, int epi, int bn, int cg, bool b_is_nk, const void* A, const void* B, const GemmArgs& args,
+int launch_kind(int kind, int epi, int bn, int cg, int rb, bool b_is_nk, const void* A, const void* B, const GemmArgs& args,
                 int64_t lda, int64_t ldb, cudaStream_t stream) {
   switch (kind) {
     case KIND_I8:
-      if (epi == EPI_I32) return launch_bn<KIND_I8, EPI_I32>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_I32) return launch_bn<KIND_I8, EPI_I32>(bn, cg, rb, b_is_nk, A, B, args, lda, ldb, stream);
       if (epi == EPI_W8A8_BF16)
-        return launch_bn<KIND_I8, EPI_W8A8_BF16>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
+        return launch_bn<KIND_I8, EPI_W8A8_BF16>(bn, cg, rb, b_is_nk, A, B, args, lda, ldb, stream);
       break;
     case KIND_F16:
-      if (epi == EPI_F16) return launch_bn<KIND_F16, EPI_F16>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
-      if (epi == EPI_F32) return launch_bn<KIND_F16, EPI_F32>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_F16) return launch_bn<KIND_F16, EPI_F16>(bn, cg, rb, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_F32) return launch_bn<KIND_F16, EPI_F32>(bn, cg, rb, b_is_nk, A, B, args, lda, ldb, stream);
       break;
     case KIND_BF16:
-      if (epi == EPI_BF16) return launch_bn<KIND_BF16, EPI_BF16>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
-      if (epi == EPI_F32) return launch_bn<KIND_BF16, EPI_F32>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_BF16) return launch_bn<KIND_BF16, EPI_BF16>(bn, cg, rb, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_F32) return launch_bn<KIND_BF16, EPI_F32>(bn, cg, rb, b_is_nk, A, B, args, lda, ldb, stream);
       break;
     case KIND_TF32:  // A and B are the stacked low/high planes made by launch_sgemm_3xtf32
-      if (epi == EPI_F32) return launch_bn<KIND_TF32, EPI_F32>(bn, cg, b_is_nk, A, B, args, lda, ldb, stream);
+      if (epi == EPI_F32) return launch_bn<KIND_TF32, EPI_F32>(bn, cg, rb, b_is_nk, A, B, args, lda, ldb, stream);
       break;
     default:
       break;

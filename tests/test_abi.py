@@ -129,7 +129,9 @@ def test_policy_knobs_and_multi_gpu_entry_points_validate_arguments(cb):
     from cudaintro_b200 import capi
 
     lib = capi.lib
-    assert lib.b200_set_tile_policy(4, 0, 0) == 1          # CTA grouping is 0, 1, 2 or 3 (the skinny kernel)
+    assert lib.b200_set_tile_policy(5, 0, 0) == 1          # CTA grouping: 0, 1, 2, 3 (the skinny kernel) or 4 (pairs, two row blocks)
+    assert lib.b200_set_tile_policy(4, 128, 0) == 1
+    assert lib.b200_set_tile_policy(4, 256, 0) == 0
     assert lib.b200_set_tile_policy(3, 64, 0) == 1         # whose tiles are 128, 192 or 256 wide
     assert lib.b200_set_tile_policy(3, 192, 0) == 0
     assert lib.b200_set_tile_policy(2, 128, 0) == 1        # CTA pairs exist for 256-wide tiles only

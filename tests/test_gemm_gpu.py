@@ -873,7 +873,7 @@ def test_kernel_gives_up_a_wait_that_cannot_end_and_the_device_stays_usable(cb, 
     torch.cuda.synchronize()
 
 
-@pytest.mark.parametrize("cg,bn", [(1, 256), (1, 128), (2, 256)])
+@pytest.mark.parametrize("cg,bn", [(1, 256), (1, 128), (2, 256), (4, 256)])
 @pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "COL_MAJOR_NN", "ROW_MAJOR_BT"])
 @pytest.mark.parametrize("shape", POLICY_SHAPES)
 def test_int8_every_tile_policy_is_bit_exact(cb, oracle, device, policy, shape, layout_name, cg, bn):
@@ -891,7 +891,7 @@ def test_int8_every_tile_policy_is_bit_exact(cb, oracle, device, policy, shape, 
     assert np.array_equal(c.cpu().numpy(), oracle_i8(oracle, cb, a, b, M, N, K, layout))
 
 
-@pytest.mark.parametrize("cg,bn", [(1, 256), (1, 64), (2, 256)])
+@pytest.mark.parametrize("cg,bn", [(1, 256), (1, 64), (2, 256), (4, 256)])
 @pytest.mark.parametrize("layout_name", ["ROW_MAJOR", "ROW_MAJOR_BT"])
 def test_16bit_and_tf32_every_tile_policy(cb, oracle, device, policy, layout_name, cg, bn):
     import torch
