@@ -1253,7 +1253,7 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
     // power cap the 16-bit gain shrinks to nothing below K = 8192 (4096^3: 126 / 134 us, 6144^3: 307 /
     // 309 us), so: tf32 (twice the bytes per flop) takes them whenever they cost at most one extra wave
     // in eight, 16-bit kinds for K >= 8192 where they cost no extra wave, int8 never.
-    if (cg == 2 && !g_multicast_call && kind != KIND_I8) {
+    if (cg == 2 && !g_multicast_call && n_dest == 1 && kind != KIND_I8) {  // several destinations: measured with 256-row tiles only
       const int64_t pairs = sms / 2;
       const int64_t tiles_n = (N + 255) / 256;
       const int64_t waves256 = (pair_tiles + pairs - 1) / pairs;
@@ -1399,7 +1399,7 @@ int launch_sgemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int
   // not by the tensor pipe: they take the kernel that splits the operands on chip (one hand-shake
   // per k-block instead of three, no scratch, one launch).  Large ones keep the split planes in
   // global memory and run on CTA pairs (measured on chip / split planes: 1024^3 29.7 / 48.4 us,
-  // 2048^3 113 / 147 us, 4096^3 797 / 725 us), except for very long sums: the pair kernel adds a
+  // 2048^3 113 / 147 us, 4096^3 797 / 640 us), except for very long sums: the pair kernel adds a
   // whole K into one accumulator, whose truncation error grows with K (9.6e-6 at K = 4096), while
   // the on-chip kernel sums K in ranges (4.9e-6 there).
   if (g_x3_path != 1 && x3_on_chip_applies(A, B, lda, ldb) &&

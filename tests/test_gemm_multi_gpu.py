@@ -68,7 +68,7 @@ def test_store_paths_leave_padding_alone(cb, device, policies, register_stores):
     g = torch.Generator(device=device).manual_seed(11)
     a = torch.randn((M, K), device=device, generator=g).to(torch.bfloat16)
     b = torch.randn((N, K), device=device, generator=g).to(torch.bfloat16)
-    for cg in (1, 2):
+    for cg in (1, 2, 4):
         set_tiles(cg, 256, 0)
         out = torch.full((M + 4, ldc), 7.0, dtype=torch.bfloat16, device=device)
         st = capi.lib.b200_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, K, K, ldc, cb.ROW_MAJOR_BT, None)
@@ -79,7 +79,7 @@ def test_store_paths_leave_padding_alone(cb, device, policies, register_stores):
         assert bool((out[:M, N:] == 7.0).all()) and bool((out[M:] == 7.0).all())
 
 
-@pytest.mark.parametrize("tiles", [(0, 0), (1, 256), (1, 128), (2, 256)])
+@pytest.mark.parametrize("tiles", [(0, 0), (1, 256), (1, 128), (2, 256), (4, 256)])
 def test_multi_destination_under_every_tiling(cb, oracle, device, policies, tiles):
     """b200_gemm_multi under every tiling it can take: all destinations (peers first, destination 0
     last) bit-exact against the oracle, twice in a row."""
