@@ -1251,14 +1251,15 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
     // 256-row / 512-row tiles: tf32 8192^3 1550 / 1306 us, 4096^3 213 / 180 us; bf16 8192^3 718 / 676 us,
     // 4096^3 99.8 / 95.5 us; int8 8192^3 339 / 339 us, 4096^3 52.6 / 55.6 us.  In long runs under the
     // power cap the 16-bit gain shrinks to nothing below K = 8192 (4096^3: 126 / 134 us, 6144^3: 307 /
-    // 309 us), so: tf32 (twice the bytes per flop) takes them whenever they cost at most one extra wave
-    // in eight, 16-bit kinds for K >= 8192 where they cost no extra wave, int8 never.
+    // 309 us); run for seconds, bf16 gains 0 / 2.7 / 4.3 % at 4096^3 / 6144^3 / 8192^3 and int8 loses
+    // 3 / 1 / 0 %.  So: tf32 (twice the bytes per flop) takes them whenever they cost at most one extra
+    // wave in eight, 16-bit kinds for K >= 6144 where they cost no extra wave, int8 never.
     if (cg == 2 && !g_multicast_call && n_dest == 1 && kind != KIND_I8) {  // several destinations: measured with 256-row tiles only
       const int64_t pairs = sms / 2;
       const int64_t tiles_n = (N + 255) / 256;
       const int64_t waves256 = (pair_tiles + pairs - 1) / pairs;
       const int64_t waves512 = 2 * ((((M + 4 * BM - 1) / (4 * BM)) * tiles_n + pairs - 1) / pairs);
-      if (kind == KIND_TF32 ? waves512 * 7 <= waves256 * 8 : (K >= 8192 && waves512 <= waves256)) rb = 2;
+      if (kind == KIND_TF32 ? waves512 * 7 <= waves256 * 8 : (K >= 6144 && waves512 <= waves256)) rb = 2;
     }
   }
   if (cg == 2) bn = 256;
