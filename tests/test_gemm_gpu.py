@@ -835,10 +835,12 @@ def test_l2_eviction_hints_do_not_change_results(cb, device):
         capi.lib.b200_set_l2_hints(-1)
 
 
-def test_kernel_gives_up_a_wait_that_cannot_end_and_the_device_stays_usable(cb, oracle, device, policy):
+@pytest.mark.parametrize("cg,M", [(1, 128), (2, 256), (4, 512)])
+def test_kernel_gives_up_a_wait_that_cannot_end_and_the_device_stays_usable(cb, oracle, device, policy, cg, M):
     """Failure handling of the tensor-core kernel itself, without any fault: the producer of a
-    single-CTA launch leaves out the loads of one k-block (b200_test_lose_arrival), so the MMA
-    lane's bounded wait for that stage runs out after the 50 ms budget given here; the CTA drains,
+    one-tile launch (a single CTA, a CTA pair, a pair with two row blocks per CTA) leaves out the
+    loads of one k-block in CTA 0 (b200_test_lose_arrival), so the MMA lane's bounded wait for that
+    stage runs out after the 50 ms budget given here; every role of every CTA gives up its own wait,
     the kernel returns, b200_check_device reports B200_ERR_DEVICE_WAIT, and the next product on the
     same context is bit-exact again."""
     import time
@@ -847,12 +849,12 @@ def test_kernel_gives_up_a_wait_that_cannot_end_and_the_device_stays_usable(cb, 
     from cudaintro_b200 import capi
 
     rng = np.random.default_rng(5)
-    M, N, K = 128, 256, 512
+    N, K = 256, 512
     a = rng.integers(-127, 128, (M, K)).astype(np.int8)
     b = rng.integers(-127, 128, (K, N)).astype(np.int8)
     ad, bd = to_dev(a, device), to_dev(b, device)
     want = oracle.gemm_i8_i32(a, b, M, N, K)
-    policy(1, 256)  # the general kernel, one CTA, one tile
+    policy(cg, 256)  # the general kernel, one tile
     assert np.array_equal(cb.gemm_i8_i32(ad, bd).cpu().numpy(), want)
     cb.check_device()
     try:
