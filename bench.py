@@ -835,7 +835,8 @@ def main():
 
 def side_measurements(device, main_workload):
     """The other types of the metric at 8192^3 (and the W8A8 linear), each timed alone: best of 10
-    single launches.  Also the vendor library's GEMM on the same shapes as a yardstick."""
+    single launches.  Also the vendor library's GEMM on the same shapes as a yardstick, its launches
+    alternating with this library's."""
     import torch
 
     from cudaintro_b200 import capi
@@ -846,33 +847,50 @@ def side_measurements(device, main_workload):
         a, b, extra = make_inputs(kind, M, N, K, device, seed=77)
         c = torch.empty((M, N), dtype=out_dtype(kind), device=device)
         what = {"bf16": capi.BF16, "f16": capi.F16, "i8": capi.I8, "w8a8": capi.W8A8}[kind]
-        for _ in range(3):
-            capi.time_gemm(what, a, b, c, M, N, K, iters=1, row_scale=extra.get("row_scale"), col_scale=extra.get("col_scale"))
-        best = min(capi.time_gemm(what, a, b, c, M, N, K, iters=1, row_scale=extra.get("row_scale"),
-                                  col_scale=extra.get("col_scale")) for _ in range(10))
+        if kind in ("bf16", "f16"):
+            vendor = lambda: torch.matmul(a, b)  # noqa: E731
+        elif kind == "i8":
+            vendor = lambda: torch._int_mm(a, b)  # noqa: E731
+        else:
+            vendor = None
+
+        def vendor_ms():
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            vendor()
+            e.record()
+            torch.cuda.synchronize()
+            return s.elapsed_time(e)
+
+        def own_ms():
+            return capi.time_gemm(what, a, b, c, M, N, K, iters=1, row_scale=extra.get("row_scale"),
+                                  col_scale=extra.get("col_scale"))
+
+        # Both implementations are warmed, then timed in turn (own, vendor, own, vendor, ...), so that
+        # neither gets the cooler or the hotter half of the measurement.
+        vendor_error = None
+        try:
+            for _ in range(3):
+                own_ms()
+                if vendor is not None:
+                    vendor()
+        except Exception as ex:  # the vendor call failing must not cost the own measurement
+            vendor_error, vendor = repr(ex)[:120], None
+        own, theirs = [], []
+        for _ in range(10):
+            own.append(own_ms())
+            if vendor is not None:
+                try:
+                    theirs.append(vendor_ms())
+                except Exception as ex:
+                    vendor_error, vendor = repr(ex)[:120], None
+        best = min(own)
         val = 2.0 * M * N * K / (best * 1e-3) / 1e12
         entry = {"value": val, "unit": unit, "ms": best, "frac_of_nominal_peak": val / NOMINAL_PEAK[kind]}
-        try:
-            if kind in ("bf16", "f16"):
-                fn = lambda: torch.matmul(a, b)  # noqa: E731
-            elif kind == "i8":
-                fn = lambda: torch._int_mm(a, b)  # noqa: E731
-            else:
-                fn = None
-            if fn is not None:
-                for _ in range(3):
-                    fn()
-                ts = []
-                for _ in range(10):
-                    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    s.record()
-                    fn()
-                    e.record()
-                    torch.cuda.synchronize()
-                    ts.append(s.elapsed_time(e))
-                entry["vendor_library"] = {"value": 2.0 * M * N * K / (min(ts) * 1e-3) / 1e12, "ms": min(ts)}
-        except Exception as ex:
-            entry["vendor_library"] = {"error": repr(ex)[:120]}
+        if vendor_error is not None:
+            entry["vendor_library"] = {"error": vendor_error}
+        elif theirs:
+            entry["vendor_library"] = {"value": 2.0 * M * N * K / (min(theirs) * 1e-3) / 1e12, "ms": min(theirs)}
         out[name] = entry
         del a, b, c, extra
         torch.cuda.empty_cache()
