@@ -260,8 +260,9 @@ def fill(t, seed: int, lo=None, hi=None):
 
 
 def set_tile_policy(cta_group: int = 0, tile_n: int = 0, group_rows: int = 0) -> None:
-    """Forces single CTAs (1), CTA pairs (2) or the K-split cluster kernel for skinny products (3), a tile
-    width and the rows per tile-order group; zeros restore the automatic choice."""
+    """Forces single CTAs (1), CTA pairs (2), CTA pairs with two row blocks per CTA (4) or the K-split
+    cluster kernel for skinny products (3), a tile width and the rows per tile-order group; zeros restore
+    the automatic choice."""
     _check(lib.b200_set_tile_policy(cta_group, tile_n, group_rows))
 
 

@@ -543,24 +543,39 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int cols_left = p.N - nb * BN;
         const int nboxes = min(BN / BOX_COLS, (cols_left + BOX_COLS - 1) / BOX_COLS);
         if constexpr (OUT_BYTES == 2) {
-          // 2-byte outputs: the warp's whole share of the tile (32 rows x 256 columns) fits in registers
-          // once converted (128 words a thread).  Convert everything first, hand the accumulators
-          // back, and only then stage and store: the MMA lane waits for the conversions alone.
+          // 2-byte outputs: the warp's whole share of the tile (32 rows x 256 columns) fits in registers and
+          // its staging buffer once converted.  Convert everything first, hand the accumulators back, and
+          // only then store: the MMA lane waits for the conversions alone.
           if (p.store_mode == STORE_TMA) {
             constexpr int NB = BN / BOX_COLS;  // 4 boxes of 64 columns
-            uint32_t packed[NB][CHUNKS_PER_BOX][16];
+            // Box 0 goes straight into the staging buffer (free since the tile before: its last store was
+            // issued a whole main loop ago), boxes 1.. wait in registers: 96 words a thread.
+            uint32_t packed[NB - 1][CHUNKS_PER_BOX][16];
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
             UW_BEGIN(w_ld);
 #pragma unroll
             for (int bx = 0; bx < NB; ++bx) {
               if (bx < nboxes) {
+                uint32_t v[CHUNKS_PER_BOX][32];
 #pragma unroll
-                for (int q = 0; q < 2 * CHUNKS_PER_BOX; ++q) {  // 16 columns at a time: few live registers beside `packed`
-                  uint32_t v[16], w[16];
-                  tmem_ld_32x16(taddr + uint32_t(bx * BOX_COLS + q * 16), v);
-                  tmem_ld_wait();
-                  pack_chunk<EPI, 16>(p, nb * BN + bx * BOX_COLS + q * 16, v, rs, w);
+                for (int h = 0; h < CHUNKS_PER_BOX; ++h) tmem_ld_32x32(taddr + uint32_t(bx * BOX_COLS + h * 32), v[h]);
+                tmem_ld_wait();
 #pragma unroll
-                  for (int i = 0; i < 8; ++i) packed[bx][q >> 1][(q & 1) * 8 + i] = w[i];
+                for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
+                  uint32_t w[32];
+                  pack_chunk<EPI>(p, nb * BN + bx * BOX_COLS + h * 32, v[h], rs, w);
+                  if (bx == 0) {
+#pragma unroll
+                    for (int i = 0; i < UNITS; ++i) {
+                      const int unit = h * UNITS + i;
+                      *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) =
+                          make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                    }
+                  } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) packed[bx > 0 ? bx - 1 : 0][h][i] = w[i];
+                  }
                 }
               }
             }
@@ -573,20 +588,23 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int bx = 0; bx < NB; ++bx) {
               if (bx < nboxes) {
                 const int n0 = nb * BN + bx * BOX_COLS;
-                UW_BEGIN(w_rd);
-                if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
-                __syncwarp();
-                UW_END(w_rd);
-                UW_BEGIN(w_cv);
+                if (bx > 0) {
+                  UW_BEGIN(w_rd);
+                  if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
+                  __syncwarp();
+                  UW_END(w_rd);
+                  UW_BEGIN(w_cv);
 #pragma unroll
-                for (int h = 0; h < CHUNKS_PER_BOX; ++h)
+                  for (int h = 0; h < CHUNKS_PER_BOX; ++h)
 #pragma unroll
-                  for (int i = 0; i < UNITS; ++i) {
-                    const int unit = h * UNITS + i;
-                    *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) = make_uint4(
-                        packed[bx][h][4 * i], packed[bx][h][4 * i + 1], packed[bx][h][4 * i + 2], packed[bx][h][4 * i + 3]);
-                  }
-                UW_END(w_cv);
+                    for (int i = 0; i < UNITS; ++i) {
+                      const int unit = h * UNITS + i;
+                      *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) =
+                          make_uint4(packed[bx > 0 ? bx - 1 : 0][h][4 * i], packed[bx > 0 ? bx - 1 : 0][h][4 * i + 1],
+                                     packed[bx > 0 ? bx - 1 : 0][h][4 * i + 2], packed[bx > 0 ? bx - 1 : 0][h][4 * i + 3]);
+                    }
+                  UW_END(w_cv);
+                }
                 UW_BEGIN(w_st);
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -1249,17 +1267,17 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
     // Two row blocks per CTA (512 x 256 tiles): a quarter fewer bytes from L2 per flop against an
     // epilogue that the next tile's MMAs no longer hide.  Measured back to back from a cool start,
     // 256-row / 512-row tiles: tf32 8192^3 1550 / 1306 us, 4096^3 213 / 180 us; bf16 8192^3 718 / 676 us,
-    // 4096^3 99.8 / 95.5 us; int8 8192^3 339 / 339 us, 4096^3 52.6 / 55.6 us.  In long runs under the
-    // power cap the 16-bit gain shrinks to nothing below K = 8192 (4096^3: 126 / 134 us, 6144^3: 307 /
-    // 309 us); run for seconds, bf16 gains 0 / 2.7 / 4.3 % at 4096^3 / 6144^3 / 8192^3 and int8 loses
-    // 3 / 1 / 0 %.  So: tf32 (twice the bytes per flop) takes them whenever they cost at most one extra
-    // wave in eight, 16-bit kinds for K >= 6144 where they cost no extra wave, int8 never.
+    // 4096^3 99.8 / 95.5 us; int8 8192^3 339 / 339 us, 4096^3 52.6 / 55.6 us.  Run for seconds under the
+    // power cap, bf16 gains 2.3 / 5.0 / 6.3 % at 4096^3 / 6144^3 / 8192^3 and int8 loses 3 / 1 / 0 %
+    // (its 4-byte outputs cannot wait in registers, so the MMA lane waits 14 % of its loop for the
+    // epilogue).  So: tf32 (twice the bytes per flop) takes them whenever they cost at most one extra
+    // wave in eight, 16-bit kinds from K = 4096 where they cost no extra wave, int8 never.
     if (cg == 2 && !g_multicast_call && n_dest == 1 && kind != KIND_I8) {  // several destinations: measured with 256-row tiles only
       const int64_t pairs = sms / 2;
       const int64_t tiles_n = (N + 255) / 256;
       const int64_t waves256 = (pair_tiles + pairs - 1) / pairs;
       const int64_t waves512 = 2 * ((((M + 4 * BM - 1) / (4 * BM)) * tiles_n + pairs - 1) / pairs);
-      if (kind == KIND_TF32 ? waves512 * 7 <= waves256 * 8 : (K >= 6144 && waves512 <= waves256)) rb = 2;
+      if (kind == KIND_TF32 ? waves512 * 7 <= waves256 * 8 : (K >= 4096 && waves512 <= waves256)) rb = 2;
     }
   }
   if (cg == 2) bn = 256;

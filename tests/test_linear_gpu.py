@@ -56,11 +56,19 @@ def test_linear_fp32_ffma_reproduces_the_reference_loops_bit_for_bit(cb, oracle,
     assert np.array_equal(got0.cpu().numpy(), oracle.linear_f32(x, w, None, out_in, relu, False, fused=True))
 
 
+@pytest.fixture
+def tile_policy(cb):
+    yield cb.set_tile_policy
+    cb.set_tile_policy(0, 0, 0)
+
+
+@pytest.mark.parametrize("tiles", [(0, 0), (4, 256)])  # automatic; CTA pairs with two row blocks (eight-warp epilogue)
 @pytest.mark.parametrize("out_in", [True, False])
 @pytest.mark.parametrize("shape", [(257, 784, 512), (100, 2048, 1024), (520, 1032, 264)])
-def test_linear_tensor_core_modes_within_tolerance(cb, oracle, device, shape, out_in):
+def test_linear_tensor_core_modes_within_tolerance(cb, oracle, device, tile_policy, shape, out_in, tiles):
     import torch
 
+    tile_policy(tiles[0], tiles[1], 0)
     batch, in_f, out_f = shape
     rng = np.random.default_rng(in_f + out_f + int(out_in))
     x = rng.standard_normal((batch, in_f)).astype(np.float32)
