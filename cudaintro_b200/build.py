@@ -3,7 +3,8 @@
     python -m cudaintro_b200.build            # build if sources are newer than the library
     python -m cudaintro_b200.build --force
     python -m cudaintro_b200.build --stamps   # measurement build: libb200gemm_stamps.so, whose skinny kernel
-                                              # records a per-k-block timeline (see cudaintro_b200/timeline.py)
+                                              # records a per-k-block timeline and whose large tensor-core
+                                              # kernel accounts for its waits (see cudaintro_b200/timeline.py)
 
 The library is a plain C-ABI shared object (see ``include/b200gemm.h``); nothing in it links
 against Python or torch.  Objects are compiled in parallel, one nvcc per source file.

@@ -2,6 +2,7 @@
 
     python -m cudaintro_b200.build --stamps      # once: the measurement build of the library
     python -m cudaintro_b200.timeline            # one JSON line per case
+    python -m cudaintro_b200.timeline --umma     # wait accounting of the large tensor-core kernel instead
 
 The measurement build (``libb200gemm_stamps.so``, compiled with ``-DB200_SKINNY_STAMPS``) makes every CTA of
 ``gemm_skinny_kernel`` record ``%globaltimer`` (32 ns resolution) for its first 64 k-blocks at four points:
@@ -104,5 +105,69 @@ def main() -> int:
     return 0
 
 
+def umma_waits() -> int:
+    """Wait accounting of the large tensor-core kernel (``python -m cudaintro_b200.timeline --umma``).
+
+    In the measurement build every CTA of ``gemm_umma_kernel`` adds up SM cycles per role: the MMA lane
+    waiting for full stages and for free accumulators and its whole loop, the producer lane waiting for
+    free stages, the epilogue from "accumulator complete" to "accumulator handed back".  One JSON line
+    per (type, shape, tiling): bf16 and int8 at 8192^3 and 4096^3 on 256-row and on 512-row CTA-pair tiles."""
+    import torch
+
+    if not os.path.exists(LIB):
+        raise SystemExit("build the measurement library first: python -m cudaintro_b200.build --stamps")
+    lib = C.CDLL(LIB)
+    lib.b200_last_error.restype = C.c_char_p
+    i64, p = C.c_int64, C.c_void_p
+    for name in ("b200_gemm_bf16", "b200_gemm_i8_i32"):
+        getattr(lib, name).argtypes = [p, p, p, i64, i64, i64, i64, i64, i64, C.c_int, p]
+    lib.b200_set_tile_policy.argtypes = [C.c_int, C.c_int, C.c_int]
+    lib.b200_debug_set_umma_waits.argtypes = [p]
+    dev = "cuda"
+    for kind in ("bf16", "int8"):
+        for n in (8192, 4096):
+            if kind == "bf16":
+                a = torch.randn((n, n), device=dev).bfloat16()
+                b = torch.randn((n, n), device=dev).bfloat16()
+                c = torch.empty((n, n), device=dev, dtype=torch.bfloat16)
+                fn = lib.b200_gemm_bf16
+            else:
+                a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
+                b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
+                c = torch.empty((n, n), device=dev, dtype=torch.int32)
+                fn = lib.b200_gemm_i8_i32
+            for cta_group, rows in ((2, 256), (4, 512)):
+                if lib.b200_set_tile_policy(cta_group, 256, 0) != 0:
+                    raise SystemExit(lib.b200_last_error().decode())
+                waits = torch.zeros((148, 16), dtype=torch.int64, device=dev)
+                for _ in range(3):
+                    if fn(a.data_ptr(), b.data_ptr(), c.data_ptr(), n, n, n, 0, 0, 0, 0, None) != 0:
+                        raise SystemExit(lib.b200_last_error().decode())
+                torch.cuda.synchronize()
+                lib.b200_debug_set_umma_waits(waits.data_ptr())
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                for _ in range(5):  # back to back: the last launch's record survives
+                    fn(a.data_ptr(), b.data_ptr(), c.data_ptr(), n, n, n, 0, 0, 0, 0, None)
+                stop.record()
+                torch.cuda.synchronize()
+                lib.b200_debug_set_umma_waits(None)
+                t = waits.cpu().double()
+                lead = t[0::2]  # the even CTA of a pair issues the MMAs
+                loop = lead[:, 2].mean().item()
+                print(json.dumps({
+                    "type": kind, "shape": [n, n, n], "tile_rows": rows,
+                    "us_per_launch": round(start.elapsed_time(stop) / 5 * 1e3, 1),
+                    "mma_loop_cycles": round(loop),
+                    "mma_waiting_full_pct": round(lead[:, 0].mean().item() / loop * 100, 1),
+                    "k_blocks_not_yet_full_when_asked": round(lead[:, 7].mean().item()),
+                    "mma_waiting_accumulator_pct": round(lead[:, 1].mean().item() / loop * 100, 1),
+                    "producer_waiting_free_stage_pct": round(t[:, 3].mean().item() / max(t[:, 4].mean().item(), 1) * 100, 1),
+                    "epilogue_complete_to_handed_back_cycles": round(t[:, 8].mean().item()),
+                }), flush=True)
+    lib.b200_set_tile_policy(0, 0, 0)
+    return 0
+
+
 if __name__ == "__main__":
-    sys.exit(main())
+    sys.exit(umma_waits() if "--umma" in sys.argv else main())
