@@ -73,7 +73,7 @@ int gemm_tensor(int kind, int epi, const void* A, const void* B, void* C, int64_
 // matrices, one stream per direction of travel plus one for the kernels, and the events that chain
 // them chunk by chunk.  Calls on one device are serialised by the workspace's lock; calls on
 // different devices do not meet.
-constexpr int kHostChunks = 16;
+constexpr int kHostChunks = 8;
 constexpr int kMaxDevices = 64;
 struct HostWorkspace {
   std::mutex mu;
@@ -161,10 +161,27 @@ int run_host_slabs(HostWorkspace& ws, int dtype, int layout, const void* whole_d
   const int64_t units = col ? N : M;                       // rows of A / columns of B
   const size_t in_unit = size_t(K) * in_elem;              // bytes of one of them
   const size_t out_unit = size_t(col ? M : N) * out_elem;  // bytes of the matching line of C
-  // Slabs of a multiple of 256 units (the tallest tile), at least 512, at most 16 of them.
-  int64_t per = (units + kHostChunks - 1) / kHostChunks;
-  per = (per + 255) / 256 * 256;
-  if (per < 512) per = 512;
+  // Slabs of a multiple of 256 units (the tallest tile of a small product), at least 512, at most 8 of them
+  // (bf16 8192^3 through b200_gemm_host_weights: 3.49 ms per call with 8 slabs, 3.63-3.71 with 4, 3.80 with 16,
+  // 4.19 with 32 of 256 rows; both directions of the host link busy at once move 43.5 GB/s each, 3.09 ms).
+  // Nothing goes down while the first slab comes up and nothing comes up while the last goes down, so where
+  // there is enough to cut, the first and the last slab are 256 units and the rest is shared by the others.
+  int64_t sizes[kHostChunks];
+  int n_slabs = 0;
+  if (units >= 8 * 512) {
+    const int middle = kHostChunks - 2;
+    int64_t per = (units - 512 + middle - 1) / middle;
+    per = (per + 255) / 256 * 256;
+    sizes[n_slabs++] = 256;
+    for (int64_t left = units - 512; left > 0 && n_slabs < kHostChunks - 1; left -= per)
+      sizes[n_slabs++] = left < per ? left : per;
+    sizes[n_slabs++] = 256;
+  } else {
+    int64_t per = (units + kHostChunks - 1) / kHostChunks;
+    per = (per + 255) / 256 * 256;
+    if (per < 512) per = 512;
+    for (int64_t left = units; left > 0; left -= per) sizes[n_slabs++] = left < per ? left : per;
+  }
 
   int rc = B200_OK;
   cudaError_t ce = cudaSuccess;
@@ -175,9 +192,9 @@ int run_host_slabs(HostWorkspace& ws, int dtype, int layout, const void* whole_d
     if (ce != cudaSuccess) what = #call;        \
   }
   if (whole_ready) HOST_STEP(cudaStreamWaitEvent(ws.stream, whole_ready, 0));
-  int i = 0;
-  for (int64_t u0 = 0; u0 < units && rc == B200_OK && ce == cudaSuccess; u0 += per, ++i) {
-    const int64_t n_units = units - u0 < per ? units - u0 : per;
+  int64_t u0 = 0;
+  for (int i = 0; i < n_slabs && rc == B200_OK && ce == cudaSuccess; u0 += sizes[i], ++i) {
+    const int64_t n_units = sizes[i];
     HOST_STEP(cudaMemcpyAsync(slab_dst + u0 * in_unit, slab_src + u0 * in_unit, size_t(n_units) * in_unit,
                               cudaMemcpyHostToDevice, ws.in_stream));
     HOST_STEP(cudaEventRecord(ws.chunk_in[i], ws.in_stream));

@@ -279,7 +279,7 @@ int b200_linear(int dtype, const void* X, const void* W, const float* bias, void
  * back, and returns after the result is in `C`.  `dtype` selects the entry point above
  * (B200_I8 -> int32 out, B200_F16 / B200_BF16 -> 16-bit out, B200_F32 -> FFMA).  The operand
  * every output line needs goes up whole (B; A for the column-major layout); the other one travels
- * in up to 16 slabs of rows (columns), each multiplied as soon as it has arrived and copied back
+ * in up to 8 slabs of rows (columns), each multiplied as soon as it has arrived and copied back
  * while the next is on its way, so with pinned buffers the call costs about its host-to-device
  * traffic.  Device workspace, three streams and their events are kept per device between calls
  * (the device that is current when the call is made) and grow as needed; b200_host_release()
