@@ -542,90 +542,96 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(group * BN);
         const int cols_left = p.N - nb * BN;
         const int nboxes = min(BN / BOX_COLS, (cols_left + BOX_COLS - 1) / BOX_COLS);
-        if constexpr (OUT_BYTES == 2) {
-          // 2-byte outputs: the warp's whole share of the tile (32 rows x 256 columns) fits in registers and
-          // its staging buffer once converted.  Convert everything first, hand the accumulators back, and
-          // only then store: the MMA lane waits for the conversions alone.
-          if (p.store_mode == STORE_TMA) {
-            constexpr int NB = BN / BOX_COLS;  // 4 boxes of 64 columns
-            // Box 0 goes straight into the staging buffer (free since the tile before: its last store was
-            // issued a whole main loop ago), boxes 1.. wait in registers: 96 words a thread.
-            uint32_t packed[NB - 1][CHUNKS_PER_BOX][16];
+        if (p.store_mode == STORE_TMA) {
+          // A box is 32 rows x 128 bytes: 32 words a thread, whatever the element size (4 boxes of 64 columns
+          // for 2-byte outputs, 8 of 32 columns for 4-byte ones).  The accumulators can go back to the MMA
+          // lane once every value has left tensor memory, so as many boxes as fit wait converted in registers
+          // (three: 96 words) and one more in the staging buffer; only the boxes before those (none for 2-byte
+          // outputs, four for 4-byte ones) are converted, staged and stored one after the other while the MMA
+          // lane waits.
+          constexpr int NB = BN / BOX_COLS;
+          constexpr int KEEP = 3;
+          constexpr int FRONT = NB - 1 - KEEP;
+          uint32_t held[KEEP][32];
+          auto buffer_free = [&]() {  // this warp's previous store has read the buffer
             if (lane == 0) tma_store_wait_read<0>();
             __syncwarp();
-            UW_BEGIN(w_ld);
+          };
+          // tensor memory -> converted words of box bx; `for_buffer`: the words go to the staging buffer next,
+          // so the wait for the buffer is spent while the tensor-memory load is in flight
+          auto load_box = [&](int bx, uint32_t (&words)[32], bool for_buffer) {
+            uint32_t v[CHUNKS_PER_BOX][32];
 #pragma unroll
-            for (int bx = 0; bx < NB; ++bx) {
-              if (bx < nboxes) {
-                uint32_t v[CHUNKS_PER_BOX][32];
+            for (int h = 0; h < CHUNKS_PER_BOX; ++h) tmem_ld_32x32(taddr + uint32_t(bx * BOX_COLS + h * 32), v[h]);
+            if (for_buffer) buffer_free();
+            tmem_ld_wait();
 #pragma unroll
-                for (int h = 0; h < CHUNKS_PER_BOX; ++h) tmem_ld_32x32(taddr + uint32_t(bx * BOX_COLS + h * 32), v[h]);
-                tmem_ld_wait();
+            for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
+              uint32_t w[32];
+              pack_chunk<EPI>(p, nb * BN + bx * BOX_COLS + h * 32, v[h], rs, w);
 #pragma unroll
-                for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
-                  uint32_t w[32];
-                  pack_chunk<EPI>(p, nb * BN + bx * BOX_COLS + h * 32, v[h], rs, w);
-                  if (bx == 0) {
-#pragma unroll
-                    for (int i = 0; i < UNITS; ++i) {
-                      const int unit = h * UNITS + i;
-                      *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) =
-                          make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-                    }
-                  } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) packed[bx > 0 ? bx - 1 : 0][h][i] = w[i];
-                  }
-                }
-              }
+              for (int i = 0; i < 32 / CHUNKS_PER_BOX; ++i) words[h * (32 / CHUNKS_PER_BOX) + i] = w[i];
             }
-            UW_END(w_ld);
-            tc_fence_before_sync();
+          };
+          auto stage_box = [&](const uint32_t (&words)[32]) {  // words -> this warp's buffer, swizzled for the store
+#pragma unroll
+            for (int unit = 0; unit < 8; ++unit)
+              *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) =
+                  make_uint4(words[4 * unit], words[4 * unit + 1], words[4 * unit + 2], words[4 * unit + 3]);
+          };
+          auto store_box = [&](int bx) {
+            const int n0 = nb * BN + bx * BOX_COLS;
+            fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[0]), 0));
-            UW_END(w_drain);
-#pragma unroll
-            for (int bx = 0; bx < NB; ++bx) {
-              if (bx < nboxes) {
-                const int n0 = nb * BN + bx * BOX_COLS;
-                if (bx > 0) {
-                  UW_BEGIN(w_rd);
-                  if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
-                  __syncwarp();
-                  UW_END(w_rd);
-                  UW_BEGIN(w_cv);
-#pragma unroll
-                  for (int h = 0; h < CHUNKS_PER_BOX; ++h)
-#pragma unroll
-                    for (int i = 0; i < UNITS; ++i) {
-                      const int unit = h * UNITS + i;
-                      *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) =
-                          make_uint4(packed[bx > 0 ? bx - 1 : 0][h][4 * i], packed[bx > 0 ? bx - 1 : 0][h][4 * i + 1],
-                                     packed[bx > 0 ? bx - 1 : 0][h][4 * i + 2], packed[bx > 0 ? bx - 1 : 0][h][4 * i + 3]);
-                    }
-                  UW_END(w_cv);
+            if (lane == 0 && row0 < p.M) {
+              if (p.n_dest > 1) {  // peers first, from a start that rotates; the local copy last
+                const int peers = p.n_dest - 1;
+                int g = 1 + int((uint32_t(first_tile) + stores) % uint32_t(peers));
+                for (int i = 0; i < peers; ++i) {
+                  tma_store_2d_hint(&tmap_c.m[g], buf, n0, row0, pol_c);
+                  if (++g == p.n_dest) g = 1;
                 }
-                UW_BEGIN(w_st);
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0 && row0 < p.M) {
-                  if (p.n_dest > 1) {  // peers first, from a start that rotates; the local copy last
-                    const int peers = p.n_dest - 1;
-                    int g = 1 + int((uint32_t(first_tile) + stores) % uint32_t(peers));
-                    for (int i = 0; i < peers; ++i) {
-                      tma_store_2d_hint(&tmap_c.m[g], buf, n0, row0, pol_c);
-                      if (++g == p.n_dest) g = 1;
-                    }
-                  }
-                  tma_store_2d_hint(&tmap_c.m[0], buf, n0, row0, pol_c);
-                  tma_store_commit();
-                }
-                UW_END(w_st);
-                ++stores;
               }
+              tma_store_2d_hint(&tmap_c.m[0], buf, n0, row0, pol_c);
+              tma_store_commit();
             }
-            continue;
+            ++stores;
+          };
+          UW_BEGIN(w_ld);
+#pragma unroll
+          for (int bx = 0; bx < FRONT; ++bx) {
+            if (bx < nboxes) {
+              uint32_t words[32];
+              load_box(bx, words, true);
+              stage_box(words);
+              store_box(bx);
+            }
           }
+          if (FRONT < nboxes) {
+            uint32_t words[32];
+            load_box(FRONT, words, true);
+            stage_box(words);
+          }
+#pragma unroll
+          for (int k = 0; k < KEEP; ++k)
+            if (FRONT + 1 + k < nboxes) load_box(FRONT + 1 + k, held[k], false);
+          UW_END(w_ld);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[0]), 0));
+          UW_END(w_drain);
+          UW_BEGIN(w_st);
+          if (FRONT < nboxes) store_box(FRONT);
+#pragma unroll
+          for (int k = 0; k < KEEP; ++k) {
+            if (FRONT + 1 + k < nboxes) {
+              buffer_free();
+              stage_box(held[k]);
+              store_box(FRONT + 1 + k);
+            }
+          }
+          UW_END(w_st);
+          continue;
         }
 #pragma unroll 1
         for (int bx = 0; bx < nboxes; ++bx) {
@@ -642,42 +648,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[0]), 0));
             UW_END(w_drain);
           }
-          if (p.store_mode == STORE_TMA) {
-            UW_BEGIN(w_rd);
-            if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
-            __syncwarp();
-            UW_END(w_rd);
-            UW_BEGIN(w_cv);
-#pragma unroll
-            for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
-              uint32_t w[32];
-              pack_chunk<EPI>(p, n0 + h * 32, v[h], rs, w);
-#pragma unroll
-              for (int i = 0; i < UNITS; ++i) {
-                const int unit = h * UNITS + i;
-                *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) =
-                    make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-              }
-            }
-            UW_END(w_cv);
-            UW_BEGIN(w_st);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0 && row0 < p.M) {
-              if (p.n_dest > 1) {  // peers first, from a start that rotates; the local copy last
-                const int peers = p.n_dest - 1;
-                int g = 1 + int((uint32_t(first_tile) + stores) % uint32_t(peers));
-                for (int i = 0; i < peers; ++i) {
-                  tma_store_2d_hint(&tmap_c.m[g], buf, n0, row0, pol_c);
-                  if (++g == p.n_dest) g = 1;
-                }
-              }
-              tma_store_2d_hint(&tmap_c.m[0], buf, n0, row0, pol_c);
-              tma_store_commit();
-            }
-            UW_END(w_st);
-            ++stores;
-          } else {
+          {  // register stores (C not aligned for TMA, or the store policy asks for them)
 #pragma unroll
             for (int h = 0; h < CHUNKS_PER_BOX; ++h) {
               uint32_t w[32];
@@ -1267,17 +1238,20 @@ int launch_umma_gemm_multi(int kind, int epi, const void* A, const void* B, void
     // Two row blocks per CTA (512 x 256 tiles): a quarter fewer bytes from L2 per flop against an
     // epilogue that the next tile's MMAs no longer hide.  Measured back to back from a cool start,
     // 256-row / 512-row tiles: tf32 8192^3 1550 / 1306 us, 4096^3 213 / 180 us; bf16 8192^3 718 / 676 us,
-    // 4096^3 99.8 / 95.5 us; int8 8192^3 339 / 339 us, 4096^3 52.6 / 55.6 us.  Run for seconds under the
-    // power cap, bf16 gains 2.3 / 5.0 / 6.3 % at 4096^3 / 6144^3 / 8192^3 and int8 loses 3 / 1 / 0 %
-    // (its 4-byte outputs cannot wait in registers, so the MMA lane waits 14 % of its loop for the
-    // epilogue).  So: tf32 (twice the bytes per flop) takes them whenever they cost at most one extra
-    // wave in eight, 16-bit kinds from K = 4096 where they cost no extra wave, int8 never.
-    if (cg == 2 && !g_multicast_call && n_dest == 1 && kind != KIND_I8) {  // several destinations: measured with 256-row tiles only
+    // 4096^3 99.8 / 95.5 us; int8 -> int32 8192^3 374 / 354 us, 4096^3 56.5 / 55.6 us.  Run for seconds
+    // under the power cap, bf16 gains 2.3 / 5.0 / 6.3 % at 4096^3 / 6144^3 / 8192^3, int8 -> int32
+    // -1 / 0.4 / 1.7 % (its 4-byte outputs leave the MMA lane waiting 11 % of its loop for the epilogue),
+    // and the W8A8 epilogue (two multiplications per value before the accumulators go back) loses 2-7 %.
+    // So: tf32 (twice the bytes per flop) takes them whenever they cost at most one extra wave in
+    // eight, 16-bit kinds from K = 4096 and int8 -> int32 from K = 8192 where they cost no extra wave,
+    // W8A8 never.
+    if (cg == 2 && !g_multicast_call && n_dest == 1 && epi != EPI_W8A8_BF16) {  // several destinations: measured with 256-row tiles only
       const int64_t pairs = sms / 2;
       const int64_t tiles_n = (N + 255) / 256;
       const int64_t waves256 = (pair_tiles + pairs - 1) / pairs;
       const int64_t waves512 = 2 * ((((M + 4 * BM - 1) / (4 * BM)) * tiles_n + pairs - 1) / pairs);
-      if (kind == KIND_TF32 ? waves512 * 7 <= waves256 * 8 : (K >= 4096 && waves512 <= waves256)) rb = 2;
+      const int64_t k_from = kind == KIND_I8 ? 8192 : 4096;
+      if (kind == KIND_TF32 ? waves512 * 7 <= waves256 * 8 : (K >= k_from && waves512 <= waves256)) rb = 2;
     }
   }
   if (cg == 2) bn = 256;

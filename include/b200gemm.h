@@ -72,7 +72,7 @@ int b200_sm_count(void);
  * of C share one sweep across N in the tile order.  0 restores the automatic choice of each.
  * CTA pairs exist for 256-wide tiles only.  cta_group = 4 is a CTA pair in which every CTA owns two
  * 128-row blocks (512 x 256 tiles, eight epilogue warps; chosen by itself for tf32 products and for
- * 16-bit products with K >= 4096 when it costs no extra wave of tiles).  cta_group = 3 sends fp16 / bf16 products of at most
+ * 16-bit products with K >= 4096 and int8 -> int32 products with K >= 8192 when it costs no extra wave of tiles).  cta_group = 3 sends fp16 / bf16 products of at most
  * 128 rows to the K-split cluster kernel (tile_n 0, 128, 192 or 256) and makes every other product
  * fail with B200_ERR_UNSUPPORTED; without a policy that kernel is chosen by itself when it lets
  * every SM stream clearly less of B.  Integer results do not depend on the policy;
