@@ -595,12 +595,19 @@ def main():
         def step():
             fused.step(what, a, b, extra.get("row_scale"), extra.get("col_scale"))
 
-        # untimed check: the fused path must assemble exactly what GEMM + NCCL all-gather assembles
+        # untimed check: the fused path must assemble what GEMM + NCCL all-gather assembles: bit for bit for
+        # the integer kinds; to rounding for the 16-bit types, whose K order depends on the tiling, and the
+        # single-destination GEMM of the NCCL path may run on other tiles than the multi-destination one
         nccl_step()
         step()
         barrier()
-        agree(torch.equal(fused.result().view(torch.uint8), sharded.result().view(torch.uint8)),
-              f"rank {rank}: fused GEMM + all-gather differs from GEMM + NCCL all-gather", world, device)
+        if kind in ("i8", "w8a8"):
+            same = torch.equal(fused.result().view(torch.uint8), sharded.result().view(torch.uint8))
+        else:
+            want = sharded.result().float()
+            same = bool((fused.result().float() - want).norm() <= 1e-2 * want.norm())
+            del want
+        agree(same, f"rank {rank}: fused GEMM + all-gather differs from GEMM + NCCL all-gather", world, device)
 
     # untimed check of the assembled C against the CPU oracle: rows from every rank's slab
     if fused is None:
