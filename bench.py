@@ -53,7 +53,7 @@ METRIC = "int8 TOPS & bf16/fp16 TFLOPS per GPU at 8192^3; % of dense tensor peak
 # dram__bytes_write.sum); None until a capture of that workload is summarised under profiles/.
 NCU_TRAFFIC_BYTES = {
     "bf16_8192": 704302000 + 139248000,   # profiles/gemm_umma_bf16_8192x8192x8192.md
-    "int8_8192": 303960576 + 241032192,   # profiles/gemm_umma_int8_8192x8192x8192.md
+    "int8_8192": 317102848 + 231789312,   # profiles/gemm_umma_int8_8192x8192x8192.md
     "w8a8": 841799424 + 458604544,        # profiles/gemm_umma_w8a8_8192x28672x8192.md
 }
 
